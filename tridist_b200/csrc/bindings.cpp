@@ -1,0 +1,208 @@
+// Python bindings (module `tridist_b200._C`).
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "ops/elementwise.h"
+#include "ops/fused_gemm.h"
+#include "ops/moe_a2a.h"
+#include "common/status.h"
+#include "runtime/symm_heap.h"
+
+namespace py = pybind11;
+using namespace tdb;
+
+static void* cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+template <typename T>
+static T get(const py::dict& d, const char* k, T dflt) {
+  if (!d.contains(k)) return dflt;
+  return d[k].cast<T>();
+}
+
+static void fill_ptrs(const py::dict& d, const char* k, int64_t* out, int n) {
+  if (!d.contains(k)) return;
+  auto v = d[k].cast<std::vector<int64_t>>();
+  for (int i = 0; i < n && i < static_cast<int>(v.size()); ++i) out[i] = v[i];
+}
+
+static void fill_ptrs2(const py::dict& d, const char* k, int64_t (*out)[8]) {
+  if (!d.contains(k)) return;
+  auto v = d[k].cast<std::vector<std::vector<int64_t>>>();
+  for (int p = 0; p < 2 && p < static_cast<int>(v.size()); ++p)
+    for (int i = 0; i < 8 && i < static_cast<int>(v[p].size()); ++i) out[p][i] = v[p][i];
+}
+
+static int64_t py_gemm_plan_create(const py::dict& d) {
+  GemmPlanDesc g;
+  g.op = get<int>(d, "op", 0);
+  g.epi = get<int>(d, "epi", 0);
+  g.sched = get<int>(d, "sched", 0);
+  g.bn = get<int>(d, "bn", 256);
+  g.bf16 = get<bool>(d, "bf16", false);
+  g.rank = get<int>(d, "rank", 0);
+  g.R = get<int>(d, "R", 1);
+  g.M = get<int>(d, "M", 0);
+  g.N = get<int>(d, "N", 0);
+  g.K = get<int>(d, "K", 0);
+  g.a = get<int64_t>(d, "a", 0);
+  g.a_rows = get<int64_t>(d, "a_rows", g.M);
+  g.lda = get<int64_t>(d, "lda", g.K);
+  g.b = get<int64_t>(d, "b", 0);
+  g.b_rows = get<int64_t>(d, "b_rows", g.N);
+  g.ldb = get<int64_t>(d, "ldb", g.K);
+  g.c = get<int64_t>(d, "c", 0);
+  g.ldc = get<int64_t>(d, "ldc", g.N);
+  g.m_per_rank = get<int>(d, "m_per_rank", 0);
+  if (d.contains("seg_order")) {
+    auto v = d["seg_order"].cast<std::vector<int>>();
+    for (size_t i = 0; i < v.size() && i < 8; ++i) g.seg_order[i] = v[i];
+  }
+  g.order_table = get<int64_t>(d, "order_table", 0);
+  g.tile_list = get<int64_t>(d, "tile_list", 0);
+  g.list_len = get<int>(d, "list_len", 0);
+  g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);
+  g.max_ctas = get<int>(d, "max_ctas", 0);
+  fill_ptrs2(d, "peer_ws", g.peer_ws);
+  fill_ptrs(d, "peer_ag_flags", g.peer_ag_flags, 8);
+  g.ag_counters = get<int64_t>(d, "ag_counters", 0);
+  g.arrival_ns = get<int64_t>(d, "arrival_ns", 0);
+  g.chunk_rows = get<int>(d, "chunk_rows", 0);
+  g.n_chunks = get<int>(d, "n_chunks", 0);
+  g.push_parts = get<int>(d, "push_parts", 0);
+  g.skip_comm = get<int>(d, "skip_comm", 0);
+  fill_ptrs2(d, "peer_slots", g.peer_slots);
+  fill_ptrs(d, "peer_tile_flags", g.peer_tile_flags, 8);
+  g.slot_stride = get<int64_t>(d, "slot_stride", 0);
+  fill_ptrs2(d, "peer_res", g.peer_res);
+  fill_ptrs(d, "peer_res_flags", g.peer_res_flags, 8);
+  g.res_is_c = get<int>(d, "res_is_c", 0);
+  g.status_dev = get<int64_t>(d, "status_dev", 0);
+  g.abort_word = get<int64_t>(d, "abort_word", 0);
+  g.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
+  return gemm_plan_create(g);
+}
+
+static MoeDesc moe_desc_from(const py::dict& d) {
+  MoeDesc m;
+  std::memset(&m, 0, sizeof(m));
+  m.rank = get<int>(d, "rank", 0);
+  m.R = get<int>(d, "R", 1);
+  m.E = get<int>(d, "E", 0);
+  m.epr = m.E / (m.R > 0 ? m.R : 1);
+  m.H = get<int>(d, "H", 0);
+  m.T = get<int>(d, "T", 0);
+  m.topk = get<int>(d, "topk", 1);
+  m.max_recv_rows = get<int>(d, "max_recv_rows", 0);
+  m.bf16 = get<bool>(d, "bf16", false) ? 1 : 0;
+  m.round = get<uint32_t>(d, "round", 0);
+  m.tokens = reinterpret_cast<const void*>(get<int64_t>(d, "tokens", 0));
+  m.topk_idx = reinterpret_cast<const int32_t*>(get<int64_t>(d, "topk_idx", 0));
+  m.topk_weights = reinterpret_cast<const float*>(get<int64_t>(d, "topk_weights", 0));
+  m.has_weights = m.topk_weights != nullptr ? 1 : 0;
+  m.output = reinterpret_cast<void*>(get<int64_t>(d, "output", 0));
+  int64_t tmp[8];
+  auto fill = [&](const char* k, auto** out) {
+    std::memset(tmp, 0, sizeof(tmp));
+    fill_ptrs(d, k, tmp, 8);
+    for (int i = 0; i < 8; ++i) out[i] = reinterpret_cast<std::remove_reference_t<decltype(out[0])>>(tmp[i]);
+  };
+  fill("peer_recv", m.peer_recv);
+  fill("peer_out", m.peer_out);
+  fill("peer_meta", m.peer_meta);
+  fill("peer_meta_flags", m.peer_meta_flags);
+  fill("peer_done_flags", m.peer_done_flags);
+  fill("peer_ready_flags", m.peer_ready_flags);
+  m.splits = reinterpret_cast<int32_t*>(get<int64_t>(d, "splits", 0));
+  m.dst_row_base = reinterpret_cast<int32_t*>(get<int64_t>(d, "dst_row_base", 0));
+  m.counters = reinterpret_cast<int32_t*>(get<int64_t>(d, "counters", 0));
+  m.recv_seg = reinterpret_cast<int32_t*>(get<int64_t>(d, "recv_seg", 0));
+  m.recv_counts = reinterpret_cast<int32_t*>(get<int64_t>(d, "recv_counts", 0));
+  m.recv_total = reinterpret_cast<int32_t*>(get<int64_t>(d, "recv_total", 0));
+  m.scatter_idx = reinterpret_cast<int32_t*>(get<int64_t>(d, "scatter_idx", 0));
+  m.done_counter = reinterpret_cast<uint32_t*>(get<int64_t>(d, "done_counter", 0));
+  m.env.status = reinterpret_cast<StatusBlock*>(get<int64_t>(d, "status_dev", 0));
+  m.env.abort_word = reinterpret_cast<uint32_t*>(get<int64_t>(d, "abort_word", 0));
+  m.env.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
+  m.env.rank = static_cast<uint32_t>(m.rank);
+  return m;
+}
+
+static torch::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> sizes, torch::ScalarType dt,
+                                     int device) {
+  auto opts = torch::TensorOptions().dtype(dt).device(torch::kCUDA, device);
+  return torch::from_blob(reinterpret_cast<void*>(ptr), sizes, [](void*) {}, opts);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "tridist_b200 native runtime: symmetric heap, fused sm_100a kernels";
+
+  // ---- symmetric heap -------------------------------------------------------
+  m.def("symm_alloc", [](int64_t bytes) { return reinterpret_cast<int64_t>(symm_alloc_local(bytes)); });
+  m.def("symm_free", [](int64_t p) { symm_free_local(reinterpret_cast<void*>(p)); });
+  m.def("symm_export", [](int64_t p) { return py::bytes(symm_export_handle(reinterpret_cast<void*>(p))); });
+  m.def("symm_open", [](py::bytes h) { return reinterpret_cast<int64_t>(symm_open_handle(std::string(h))); });
+  m.def("symm_close", [](int64_t p) { symm_close_handle(reinterpret_cast<void*>(p)); });
+  m.def("enable_peer_access", &symm_enable_peer_access);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+
+  // ---- status plane -----------------------------------------------------------
+  m.def("status_alloc", [] {
+    MappedStatus s = status_alloc();
+    return std::make_pair(reinterpret_cast<int64_t>(s.host_ptr), reinterpret_cast<int64_t>(s.dev_ptr));
+  });
+  m.def("status_free", [](int64_t h) {
+    status_free(MappedStatus{reinterpret_cast<StatusBlock*>(h), nullptr});
+  });
+  m.def("status_read", [](int64_t h) {
+    const volatile uint32_t* w = reinterpret_cast<const volatile uint32_t*>(h);
+    return std::vector<uint32_t>{w[0], w[1], w[2], w[3], w[4], w[5]};
+  });
+  m.def("status_clear", [](int64_t h) {
+    volatile uint32_t* w = reinterpret_cast<volatile uint32_t*>(h);
+    for (int i = 0; i < 8; ++i) w[i] = 0;
+  });
+
+  // ---- fused GEMM family --------------------------------------------------------
+  m.def("gemm_plan_create", &py_gemm_plan_create);
+  m.def("gemm_plan_destroy", &gemm_plan_destroy);
+  m.def("gemm_plan_launch", [](int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm) {
+    gemm_plan_launch(id, round, parity, order_table, skip_comm, cur_stream());
+  });
+  m.def("gemm_plans_launch_emulated",
+        [](std::vector<int64_t> ids, uint32_t round, int parity, int skip_comm) {
+          gemm_plans_launch_emulated(ids, round, parity, skip_comm, cur_stream());
+        });
+  m.def("launch_count", &launch_count);
+
+  // ---- small kernels --------------------------------------------------------------
+  m.def("swiglu", [](int64_t h, int64_t out, int64_t rows, int64_t inter, int64_t ldh, bool bf16) {
+    swiglu_launch(reinterpret_cast<const void*>(h), reinterpret_cast<void*>(out), rows, inter, ldh, bf16,
+                  cur_stream());
+  });
+  m.def("barrier_all", [](std::vector<int64_t> peer_slots, int rank, int R, uint32_t ticket, int64_t status_dev,
+                          int64_t abort_word, uint64_t timeout_ns) {
+    barrier_launch(peer_slots, rank, R, ticket, status_dev, abort_word, timeout_ns, cur_stream());
+  });
+  m.def("wait_flag_test", [](int64_t flag, uint32_t ticket, int64_t status_dev, int64_t abort_word,
+                             uint64_t timeout_ns) {
+    wait_flag_test_launch(flag, ticket, status_dev, abort_word, timeout_ns, cur_stream());
+  });
+  m.def("fill_u32", [](int64_t p, int64_t n, uint32_t v) {
+    fill_u32_launch(reinterpret_cast<uint32_t*>(p), n, v, cur_stream());
+  });
+  m.def("spot_verify", [](int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                          bool bf16, int spots, float tol, int64_t bad_tiles, int bn) {
+    spot_verify_launch(a, b, c, M, N, K, lda, ldb, ldc, bf16, spots, tol, bad_tiles, bn, cur_stream());
+  });
+
+  // ---- MoE all-to-all ----------------------------------------------------------------
+  m.def("moe_meta", [](const py::dict& d) { moe_meta_launch(moe_desc_from(d), cur_stream()); });
+  m.def("moe_dispatch", [](const py::dict& d) { moe_dispatch_launch(moe_desc_from(d), cur_stream()); });
+  m.def("moe_combine", [](const py::dict& d) { moe_combine_launch(moe_desc_from(d), cur_stream()); });
+  m.def("moe_emulated", [](std::vector<py::dict> ds, int phase) {
+    std::vector<MoeDesc> v;
+    for (auto& d : ds) v.push_back(moe_desc_from(d));
+    moe_emulated_launch(v, phase, cur_stream());
+  });
+}

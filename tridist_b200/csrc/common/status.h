@@ -1,0 +1,51 @@
+// Error-status records shared by host and device code (no device intrinsics here).
+#pragma once
+#include <cstdint>
+
+namespace tdb {
+
+enum StatusCode : uint32_t {
+  ST_OK = 0,
+  ST_TIMEOUT_FLAG = 1,     // a cross-rank flag did not reach its ticket in time
+  ST_TIMEOUT_MBAR = 2,     // an intra-CTA pipeline barrier did not flip in time
+  ST_BAD_INDEX = 3,        // a computed row / tile / offset was out of range
+  ST_OVERFLOW = 4,         // a receive buffer would be oversubscribed
+};
+
+// Wait sites (the `site` word of the record).
+enum WaitSite : uint32_t {
+  SITE_AG_CHUNK = 1,
+  SITE_RS_TILE = 2,
+  SITE_AR_TILE = 3,
+  SITE_AR_RESULT = 4,
+  SITE_BARRIER = 5,
+  SITE_MOE_META = 6,
+  SITE_MOE_DISPATCH_DONE = 7,
+  SITE_MOE_COMBINE_READY = 8,
+  SITE_PIPE_FULL = 16,
+  SITE_PIPE_EMPTY = 17,
+  SITE_TMEM_FULL = 18,
+  SITE_TMEM_EMPTY = 19,
+  SITE_TEST = 32,
+};
+
+// Lives in pinned, device-mapped host memory: the host can poll it without a
+// stream synchronisation. Written only on failure.
+struct StatusBlock {
+  uint32_t code;
+  uint32_t rank;
+  uint32_t site;
+  uint32_t expected;
+  uint32_t seen;
+  uint32_t aux;
+  uint32_t pad[2];
+};
+
+struct WaitEnv {
+  StatusBlock* status;      // mapped host memory (may be nullptr)
+  uint32_t* abort_word;     // device memory, one word per context; non-zero = give up
+  uint64_t timeout_ns;      // limit for a single wait
+  uint32_t rank;
+};
+
+}  // namespace tdb

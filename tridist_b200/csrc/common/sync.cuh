@@ -1,0 +1,76 @@
+// Bounded waits and the error-status plane shared by every kernel.
+//
+// No kernel in this library spins without a limit. A wait that runs out writes
+// one record {code, rank, site, expected, seen, aux} to the context's status
+// block (first writer wins), raises the context-wide abort word that every
+// other wait polls, and returns false; callers unwind to their teardown (free
+// TMEM, fall through the final CTA barrier) and the kernel ends normally, so
+// the CUDA context stays usable and the host can raise a Python exception.
+#pragma once
+#include "ptx.cuh"
+#include "status.h"
+
+namespace tdb {
+
+__device__ __forceinline__ void report_failure(const WaitEnv& env, uint32_t code, uint32_t site,
+                                               uint32_t expected, uint32_t seen, uint32_t aux) {
+  if (env.abort_word) atomicExch(env.abort_word, code);
+  if (env.status) {
+    if (atomicCAS_system(&env.status->code, 0u, code) == 0u) {
+      env.status->rank = env.rank;
+      env.status->site = site;
+      env.status->expected = expected;
+      env.status->seen = seen;
+      env.status->aux = aux;
+      __threadfence_system();
+    }
+  }
+}
+
+__device__ __forceinline__ bool aborted(const WaitEnv& env) {
+  return env.abort_word != nullptr && *reinterpret_cast<volatile uint32_t*>(env.abort_word) != 0u;
+}
+
+// Spin until *flag >= ticket (monotonic tickets; wrap-safe signed difference).
+// The successful read is an acquire at system scope.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t ticket,
+                                             const WaitEnv& env, uint32_t site, uint32_t aux) {
+  uint32_t v = ld_acquire_sys(flag);
+  if (static_cast<int32_t>(v - ticket) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    v = ld_acquire_sys(flag);
+    if (static_cast<int32_t>(v - ticket) >= 0) return true;
+    if ((++it & 63u) == 0u) {
+      if (aborted(env)) return false;
+      if (globaltimer_ns() - t0 > env.timeout_ns) {
+        report_failure(env, ST_TIMEOUT_FLAG, site, ticket, v, aux);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// Wait for an mbarrier phase with the same limit.
+__device__ __forceinline__ bool wait_mbar(uint64_t* bar, uint32_t parity, const WaitEnv& env,
+                                          uint32_t site, uint32_t aux) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 31u) == 0u) {
+      if (aborted(env)) return false;
+      if (globaltimer_ns() - t0 > env.timeout_ns) {
+        report_failure(env, ST_TIMEOUT_MBAR, site, parity, 0u, aux);
+        return false;
+      }
+    }
+  }
+}
+
+}  // namespace tdb

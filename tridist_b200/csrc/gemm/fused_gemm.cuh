@@ -1,0 +1,731 @@
+// One persistent sm_100a kernel serves the plain GEMM and the three fused
+// communication+GEMM operators:
+//
+//   OP_PLAIN   C = A @ B^T
+//   OP_AG      C = allgather_M(A) @ B^T     comm warps push this rank's A shard into every
+//                                           peer's workspace and raise per-(source, chunk)
+//                                           tickets; the TMA warp gates each remote row
+//                                           block on its ticket before loading it
+//   OP_RS      out_r = rows r of sum_s A_s @ B_s^T
+//                                           the epilogue stores partial tiles straight into
+//                                           the owner rank's per-source slot; tiles of the
+//                                           rank's own rows are reduced in the epilogue
+//                                           (fp32) from the slots the peers filled
+//   OP_AR1     one-shot all-reduce: every partial tile goes to all peers, each rank reduces
+//   OP_AR2     two-shot all-reduce: tile owner reduces, broadcasts the reduced tile
+//
+// Roles inside one CTA (320 threads, one CTA per SM):
+//   warp 0      TMA producer (one lane): smem ring of kStages {A 128x64, B BNx64} tiles
+//   warp 1      tcgen05.mma issuer (one lane), owns the TMEM allocation (2 accumulators)
+//   warps 2-5   epilogue: tcgen05.ld -> convert -> global / peer stores (+ in-epilogue reduce)
+//   warps 6-9   communication warps (AG push, AR2 result copy); idle otherwise
+//
+// Reference behaviour covered (file paths inside the reference project):
+//   triton_dist/kernels/dcu/all_gather_gemm.py:98-230   consumer GEMM gated on flags
+//   triton_dist/kernels/dcu/all_gather_gemm.py:265-314  all-gather push + signalling
+//   triton_dist/kernels/dcu/gemm_reduce_scatter.py:39-135 GEMM, scatter, reduce
+//   triton_dist/kernels/dcu/gemm_allreduce.py:73-181    producer GEMM + consumer reduce
+//   triton_dist/kernels/dcu/ag_tr_pred.py:344-361       table-driven tile order
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../common/ptx.cuh"
+#include "../common/sync.cuh"
+
+namespace tdb {
+
+constexpr int kMaxRanks = 8;
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 x 2 B = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 320;
+constexpr int kEpiWarp0 = 2;
+constexpr int kCommWarp0 = 6;
+constexpr int kCommThreads = 128;
+constexpr int kEpiThreads = 128;
+
+enum GemmOp : int32_t { OP_PLAIN = 0, OP_AG = 1, OP_RS = 2, OP_AR1 = 3, OP_AR2 = 4 };
+enum EpiMode : int32_t { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum SchedMode : int32_t {
+  SCHED_NATURAL = 0,   // grouped raster over the whole tile grid
+  SCHED_SEGMENT = 1,   // R row segments visited in seg_order (AG sources / RS owners)
+  SCHED_STRIDED = 2,   // tile owner = linear id % R, owners visited in seg_order (AR2)
+  SCHED_LIST = 3,      // explicit list of row-major tile ids (repair of flagged tiles)
+};
+
+template <int BN>
+struct TileShape {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  // ring + 1 KB for barriers and the TMEM slot + 1 KB alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+};
+
+struct alignas(64) GemmParams {
+  CUtensorMap tma_a;       // A [rows, K]; for OP_AG this rank's local shard [M_pr, K]
+  CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
+  CUtensorMap tma_b;       // B [N_rows, K], box 128 rows
+
+  int32_t M, N, K;         // output is M x N (for EPI_SWIGLU: M x N with B holding 2N rows)
+  int32_t m_tiles, n_tiles, k_blocks;
+  int32_t rank, R;
+  int32_t op, epi, sched;
+  int32_t seg_m_tiles;     // m-tiles per segment (SCHED_SEGMENT)
+  int32_t seg_order[kMaxRanks];
+  const int32_t* order_table;  // optional device table overriding seg_order (R entries)
+  const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
+  int32_t list_len;
+  int32_t m_per_rank;      // rows per rank (AG source shard / RS owner block)
+  int32_t swiglu_up_row0;  // EPI_SWIGLU: row offset of the "up" half inside B
+  int32_t is_bf16;
+  uint32_t round;          // monotonic ticket of this call
+
+  void* c;                 // local output (see per-op meaning in the kernel)
+  int64_t ldc;
+
+  // ---- OP_AG ----
+  const void* a_local;             // this rank's shard (push source)
+  void* peer_ws[kMaxRanks];        // workspace base (this round's parity) on every rank
+  uint32_t* peer_ag_flags[kMaxRanks];  // [R][n_chunks] tickets on every rank, indexed by source
+  uint32_t* ag_counters;           // local [R][n_chunks] part counters
+  uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
+  int32_t chunk_rows, n_chunks, push_parts;
+  int32_t skip_comm;
+
+  // ---- OP_RS / OP_AR* ----
+  void* peer_slots[kMaxRanks];     // slot base (this round's parity) on every rank: [R][rows][N]
+  uint32_t* peer_tile_flags[kMaxRanks];  // [R][tiles] tickets on every rank, indexed by source
+  int64_t slot_stride;             // elements between two sources' slots
+  void* peer_res[kMaxRanks];       // OP_AR2: reduced-result buffer [M][N] on every rank
+  uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [tiles] tickets
+  int32_t res_is_c;                // OP_AR2: caller's c aliases peer_res[rank]; skip the copy
+
+  WaitEnv env;
+  int32_t pad_[2];
+};
+
+// ----------------------------------------------------------------------------
+// Tile order
+// ----------------------------------------------------------------------------
+struct TileCoord {
+  int m_tile, n_tile, linear;
+  bool valid;
+};
+
+__device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, int& mt, int& nt) {
+  // Groups of 8 m-tiles walked column by column: a wave of CTAs shares few A
+  // row blocks and a contiguous run of B column blocks in L2.
+  constexpr int G = 8;
+  const int per_group = G * n_tiles;
+  const int g = u / per_group;
+  const int first_m = g * G;
+  const int gm = min(G, m_tiles - first_m);
+  const int r = u - g * per_group;
+  mt = first_m + r % gm;
+  nt = r / gm;
+}
+
+__device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos) {
+  TileCoord t;
+  t.valid = true;
+  if (p.sched == SCHED_SEGMENT) {
+    const int per_seg = p.seg_m_tiles * p.n_tiles;
+    const int si = pos / per_seg;
+    const int u = pos - si * per_seg;
+    int mt, nt;
+    raster_grouped(u, p.seg_m_tiles, p.n_tiles, mt, nt);
+    t.m_tile = order[si] * p.seg_m_tiles + mt;
+    t.n_tile = nt;
+  } else if (p.sched == SCHED_STRIDED) {
+    const int total = p.m_tiles * p.n_tiles;
+    const int per_owner = (total + p.R - 1) / p.R;
+    const int oi = pos / per_owner;
+    const int k = pos - oi * per_owner;
+    const int lin = order[oi] + k * p.R;
+    if (lin >= total) {
+      t.valid = false;
+      t.m_tile = t.n_tile = 0;
+    } else {
+      raster_grouped(lin, p.m_tiles, p.n_tiles, t.m_tile, t.n_tile);
+    }
+    // ownership and tickets are keyed by the pre-raster id (owner = id % R)
+    t.linear = lin;
+    return t;
+  } else if (p.sched == SCHED_LIST) {
+    const int lin = p.tile_list[pos];
+    t.valid = lin >= 0 && lin < p.m_tiles * p.n_tiles;
+    t.m_tile = t.valid ? lin / p.n_tiles : 0;
+    t.n_tile = t.valid ? lin - t.m_tile * p.n_tiles : 0;
+  } else {
+    raster_grouped(pos, p.m_tiles, p.n_tiles, t.m_tile, t.n_tile);
+  }
+  t.linear = t.m_tile * p.n_tiles + t.n_tile;
+  return t;
+}
+
+__device__ __forceinline__ int sched_positions(const GemmParams& p) {
+  const int total = p.m_tiles * p.n_tiles;
+  if (p.sched == SCHED_STRIDED) return ((total + p.R - 1) / p.R) * p.R;
+  if (p.sched == SCHED_LIST) return p.list_len;
+  return total;
+}
+
+// ----------------------------------------------------------------------------
+// Epilogue helpers
+// ----------------------------------------------------------------------------
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+  if constexpr (kBf16) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+}
+
+// Adds 32 consecutive 16-bit values at `src` (64 bytes, not cached in L1) to acc.
+template <bool kBf16>
+__device__ __forceinline__ void add_row32(float (&acc)[32], const void* src) {
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 v = ld_global_cg_v4(s + q);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack2<kBf16>(w[j]);
+      acc[q * 8 + j * 2] += f.x;
+      acc[q * 8 + j * 2 + 1] += f.y;
+    }
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void store_row32(void* dst, const float (&acc)[32]) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 v;
+    v.x = pack2<kBf16>(acc[q * 8 + 0], acc[q * 8 + 1]);
+    v.y = pack2<kBf16>(acc[q * 8 + 2], acc[q * 8 + 3]);
+    v.z = pack2<kBf16>(acc[q * 8 + 4], acc[q * 8 + 5]);
+    v.w = pack2<kBf16>(acc[q * 8 + 6], acc[q * 8 + 7]);
+    st_global_v4(d + q, v);
+  }
+}
+
+// Rounds the accumulator through the 16-bit output type (so that a value every
+// rank re-derives from the same 16-bit partials is bit-identical everywhere).
+template <bool kBf16>
+__device__ __forceinline__ void round_row32(float (&acc)[32]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float2 f = unpack2<kBf16>(pack2<kBf16>(acc[2 * j], acc[2 * j + 1]));
+    acc[2 * j] = f.x;
+    acc[2 * j + 1] = f.y;
+  }
+}
+
+// Collective decision of the four epilogue warps. The flag is sticky; the
+// second barrier keeps a fast warp from raising it for a later check while a
+// slow warp has not read it yet, so all 128 threads always agree.
+__device__ __forceinline__ bool epi_vote(volatile int32_t* flag, bool my_ok) {
+  if (!my_ok) *flag = 1;
+  named_bar_sync(2, kEpiThreads);
+  const bool dead = *flag != 0;
+  named_bar_sync(2, kEpiThreads);
+  return !dead;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// ----------------------------------------------------------------------------
+// The kernel
+// ----------------------------------------------------------------------------
+template <int BN, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __restrict__ pv) {
+  using TS = TileShape<BN>;
+  // With pv != nullptr the launch emulates several ranks on one GPU: grid.y
+  // indexes the rank and each rank reads its own parameter block.
+  const GemmParams& p = pv ? pv[blockIdx.y] : p0;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TS::kStages * TS::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + TS::kStages;
+  uint64_t* tmem_full_bar = bars + 2 * TS::kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint64_t* drain_bar = tmem_empty_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  int32_t* s_order = reinterpret_cast<int32_t*>(tmem_slot + 4);
+  // s_flags[0]: an epilogue warp gave up; s_flags[1]: outcome of the comm warps' last wait
+  volatile int32_t* s_flags = s_order + kMaxRanks;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TS::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 4);
+    }
+    mbar_init(drain_bar, 1);
+    s_flags[0] = 0;
+    s_flags[1] = 1;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < kMaxRanks) {
+    const int i = threadIdx.x;
+    s_order[i] = (p.order_table != nullptr && i < p.R) ? p.order_table[i] : p.seg_order[i];
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TS::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int positions = sched_positions(p);
+  const WaitEnv env = p.env;
+
+  // ==========================================================================
+  // warp 0: TMA producer
+  // ==========================================================================
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&p.tma_a);
+      tma_prefetch_desc(&p.tma_b);
+      if (p.op == OP_AG) tma_prefetch_desc(&p.tma_a_ws);
+      uint32_t stage = 0, phase = 0;
+      uint32_t ready_mask[kMaxRanks] = {0};   // chunks of each source already observed
+      uint32_t pending = 0;                   // stages with a load in flight (bitmask)
+      bool ok = true;
+      for (int pos = blockIdx.x; ok && pos < positions; pos += gridDim.x) {
+        const TileCoord t = tile_at(p, s_order, pos);
+        if (!t.valid) continue;
+        const int m0 = t.m_tile * BM;
+        const int n0 = t.n_tile * BN;
+        const CUtensorMap* amap = &p.tma_a;
+        int a_row = m0;
+        if (p.op == OP_AG) {
+          const int src = m0 / p.m_per_rank;
+          if (src == p.rank) {
+            a_row = m0 - p.rank * p.m_per_rank;
+          } else {
+            amap = &p.tma_a_ws;
+            if (!p.skip_comm) {
+              // every chunk the 128-row block touches must have landed
+              const int r_lo = m0 - src * p.m_per_rank;
+              const int r_hi = min(r_lo + BM, p.m_per_rank) - 1;
+              for (int ck = r_lo / p.chunk_rows; ok && ck <= r_hi / p.chunk_rows; ++ck) {
+                if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
+                const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.n_chunks + ck;
+                ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck);
+                if (ok) {
+                  if (ck < 32) ready_mask[src] |= 1u << ck;
+                  if (p.arrival_ns != nullptr && ck == 0 && blockIdx.x == 0)
+                    p.arrival_ns[src] = globaltimer_ns();
+                }
+              }
+              if (!ok) break;
+              // remote generic-proxy stores observed through the acquire above are
+              // ordered before the async-proxy (TMA) reads below
+              fence_proxy_async_all();
+            }
+          }
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
+          if (!ok) break;
+          pending &= ~(1u << stage);
+          uint8_t* sa = ring + stage * TS::kStageBytes;
+          uint8_t* sb = sa + TS::kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], TS::kStageBytes);
+          tma_load_2d(sa, amap, &full_bar[stage], kb * BK, a_row);
+          if (p.epi == EPI_SWIGLU) {
+            // gate rows and the matching up rows form one BN-wide virtual tile
+            tma_load_2d(sb, &p.tma_b, &full_bar[stage], kb * BK, t.n_tile * (BN / 2));
+            tma_load_2d(sb + (BN / 2) * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
+                        p.swiglu_up_row0 + t.n_tile * (BN / 2));
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_2d(sb + h * 128 * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
+                          n0 + h * 128);
+          }
+          pending |= 1u << stage;
+          if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: let the loads already issued land before the CTA's shared
+        // memory is released (each such wait is itself bounded).
+        for (int s = 0; s < TS::kStages; ++s) {
+          if (!((pending >> s) & 1u)) continue;
+          // the stage was armed in the most recent pass over slot s
+          const uint32_t par = (s < static_cast<int>(stage)) ? phase : (phase ^ 1u);
+          WaitEnv quiet = env;
+          quiet.status = nullptr;
+          quiet.abort_word = nullptr;
+          wait_mbar(&full_bar[s], par, quiet, SITE_PIPE_FULL, s);
+        }
+      }
+    }
+  }
+  // ==========================================================================
+  // warp 1: MMA issuer
+  // ==========================================================================
+  else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBf16, BM, BN);
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int pos = blockIdx.x; ok && pos < positions; pos += gridDim.x) {
+        const TileCoord t = tile_at(p, s_order, pos);
+        if (!t.valid) continue;
+        const int buf = it & 1;
+        const uint32_t use = static_cast<uint32_t>(it >> 1);
+        ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(ring + stage * TS::kStageBytes);
+          const uint32_t sb = sa + TS::kABytes;
+          const uint64_t da = umma_desc_k_sw128(sa);
+          const uint64_t db = umma_desc_k_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // +32 bytes per K step inside the 128-byte swizzle row
+            umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // frees the smem stage when these MMAs retire
+          if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[buf]);   // accumulator complete
+        ++it;
+      }
+      if (!ok) {
+        // Unwinding: MMAs already issued must retire before TMEM is freed.
+        umma_commit(drain_bar);
+        WaitEnv quiet = env;
+        quiet.status = nullptr;
+        quiet.abort_word = nullptr;
+        wait_mbar(drain_bar, 0u, quiet, SITE_TMEM_FULL, 0);
+      }
+    }
+  }
+  // ==========================================================================
+  // warps 2-5: epilogue
+  // ==========================================================================
+  else if (warp < kCommWarp0) {
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int etid = (warp - kEpiWarp0) * 32 + lane;
+    const int64_t ldc = p.ldc;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const bool multi = p.R > 1;
+    int it = 0;
+    for (int pos = blockIdx.x; pos < positions; pos += gridDim.x) {
+      const TileCoord t = tile_at(p, s_order, pos);
+      if (!t.valid) continue;
+      const int buf = it & 1;
+      const uint32_t use = static_cast<uint32_t>(it >> 1);
+      // The four epilogue warps decide together whether to go on: a warp that
+      // gave up must never leave the others parked at a named barrier.
+      if (!epi_vote(&s_flags[0],
+                    wait_mbar(&tmem_full_bar[buf], use & 1u, env, SITE_TMEM_FULL, buf)))
+        break;
+      tc_fence_after_sync();
+
+      const int row = t.m_tile * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(buf * BN);
+
+      // ---- routing: which rank keeps this lane's row / this tile --------------
+      int owner = p.rank;
+      bool tile_reduces = false;            // uniform over the CTA
+      int o_lo = 0, o_hi = 0;
+      if (multi) {
+        if (p.op == OP_RS) {
+          owner = min(row / p.m_per_rank, p.R - 1);
+          o_lo = (t.m_tile * BM) / p.m_per_rank;
+          o_hi = min((min(t.m_tile * BM + BM, p.M) - 1) / p.m_per_rank, p.R - 1);
+          tile_reduces = (o_lo <= p.rank && p.rank <= o_hi);
+        } else if (p.op == OP_AR2) {
+          owner = t.linear % p.R;
+          tile_reduces = (owner == p.rank);
+        } else if (p.op == OP_AR1) {
+          tile_reduces = true;
+        }
+      }
+
+      if (multi && p.op == OP_AR1) {
+        // one-shot: publish the 16-bit partial into every rank's slot (own included)
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = t.n_tile * BN + c * 32;
+          if (row_ok && col < p.N) {
+            float acc[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+            const int64_t off = static_cast<int64_t>(row) * p.N + col;
+            for (int d = 0; d < p.R; ++d) {
+              uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
+                              (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
+              store_row32<kBf16>(slot, acc);
+            }
+          }
+        }
+        fence_acq_rel_sys();
+        named_bar_sync(2, kEpiThreads);
+        if (etid < p.R && etid != p.rank)
+          st_release_sys(p.peer_tile_flags[etid] + p.rank * tiles + t.linear, p.round);
+      }
+
+      if (tile_reduces) {
+        // every other source's partial of this tile must have landed here
+        bool ok = true;
+        if (etid == 0) {
+          for (int s = 0; ok && s < p.R; ++s) {
+            if (s == p.rank) continue;
+            ok = wait_flag_ge(p.peer_tile_flags[p.rank] + s * tiles + t.linear, p.round, env,
+                              p.op == OP_RS ? SITE_RS_TILE : SITE_AR_TILE, (s << 24) | t.linear);
+          }
+        }
+        // the barriers inside the vote also order the slot reads after the acquire
+        if (!epi_vote(&s_flags[0], ok)) break;
+      }
+
+      for (int c = 0; c < BN / 32; ++c) {
+        if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
+        float acc[32];
+        if (multi && p.op == OP_AR1) {
+          // all R contributions (own included) are summed from their 16-bit form
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+        } else if (p.epi == EPI_SWIGLU) {
+          // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, g);
+          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = silu(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+        } else {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+        }
+        const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
+                                               : t.n_tile * BN + c * 32;
+        if (!row_ok || ocol >= p.N) continue;
+
+        if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
+          store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                 (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                             acc);
+        } else if (p.op == OP_RS) {
+          const int lrow = row - owner * p.m_per_rank;
+          if (owner == p.rank) {
+            // fixed source order keeps the sum deterministic
+            for (int s = 0; s < p.R; ++s) {
+              if (s == p.rank) continue;
+              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                                    (static_cast<int64_t>(s) * p.slot_stride +
+                                     static_cast<int64_t>(lrow) * p.N + ocol) * 2;
+              add_row32<kBf16>(acc, slot);
+            }
+            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                   (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
+                               acc);
+          } else {
+            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
+                            (static_cast<int64_t>(p.rank) * p.slot_stride +
+                             static_cast<int64_t>(lrow) * p.N + ocol) * 2;
+            store_row32<kBf16>(slot, acc);
+          }
+        } else if (p.op == OP_AR1) {
+          const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+          for (int s = 0; s < p.R; ++s) {
+            const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                                  (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
+            add_row32<kBf16>(acc, slot);
+          }
+          store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                 (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                             acc);
+        } else {  // OP_AR2
+          const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+          if (owner == p.rank) {
+            for (int s = 0; s < p.R; ++s) {
+              if (s == p.rank) continue;
+              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                                    (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
+              add_row32<kBf16>(acc, slot);
+            }
+            for (int d = 0; d < p.R; ++d) {
+              if (d == p.rank && !p.res_is_c) continue;
+              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.peer_res[d]) + off * 2, acc);
+            }
+            if (!p.res_is_c)
+              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                     (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                                 acc);
+          } else {
+            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
+                            (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
+            store_row32<kBf16>(slot, acc);
+          }
+        }
+      }
+
+      // accumulator drained: hand the TMEM buffer back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+
+      // ---- publish what this tile wrote into other ranks ----------------------
+      if (multi && (p.op == OP_RS || p.op == OP_AR2)) {
+        fence_acq_rel_sys();
+        named_bar_sync(2, kEpiThreads);
+        if (p.op == OP_RS) {
+          const int o = o_lo + etid;
+          if (o <= o_hi && o != p.rank)
+            st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + t.linear, p.round);
+        } else if (owner != p.rank) {
+          if (etid == 0)
+            st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + t.linear, p.round);
+        } else if (etid < p.R && etid != p.rank) {
+          st_release_sys(p.peer_res_flags[etid] + t.linear, p.round);
+        }
+      }
+      ++it;
+    }
+  }
+  // ==========================================================================
+  // warps 6-9: communication
+  // ==========================================================================
+  else {
+    const int ctid = threadIdx.x - kCommWarp0 * 32;
+    if (p.op == OP_AG && p.R > 1 && !p.skip_comm) {
+      // Push this rank's shard to every peer, nearest-next rank first, so that
+      // at any moment each rank receives from exactly one sender. One work item
+      // is one `part` of one chunk for one destination.
+      const int64_t chunk_bytes = static_cast<int64_t>(p.chunk_rows) * p.K * 2;
+      const int64_t part_bytes = chunk_bytes / p.push_parts;   // host guarantees % 16 == 0
+      const int items_per_dest = p.n_chunks * p.push_parts;
+      const int items = (p.R - 1) * items_per_dest;
+      const int gx = gridDim.x;
+      for (int item = blockIdx.x; item < items; item += gx) {
+        const int di = item / items_per_dest;
+        const int rem = item - di * items_per_dest;
+        const int ck = rem / p.push_parts;
+        const int part = rem - ck * p.push_parts;
+        const int dest = (p.rank + 1 + di) % p.R;
+        const int64_t src_off = ck * chunk_bytes + part * part_bytes;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a_local) + src_off;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_ws[dest]) +
+                       static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2 + src_off;
+        const int64_t n16 = part_bytes >> 4;
+        int64_t i = ctid;
+        for (; i + 7 * kCommThreads < n16; i += 8 * kCommThreads) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = ld_global_nc_v4(src + ((i + u * kCommThreads) << 4));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) st_global_v4(dst + ((i + u * kCommThreads) << 4), v[u]);
+        }
+        for (; i < n16; i += kCommThreads) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
+        fence_acq_rel_sys();
+        named_bar_sync(1, kCommThreads);
+        if (ctid == 0) {
+          uint32_t* cnt = p.ag_counters + dest * p.n_chunks + ck;
+          const uint32_t old = atomicAdd(cnt, 1u);
+          if (old + 1u == static_cast<uint32_t>(p.push_parts)) {
+            atomicExch(cnt, 0u);
+            fence_acq_rel_sys();
+            st_release_sys(p.peer_ag_flags[dest] + p.rank * p.n_chunks + ck, p.round);
+          }
+        }
+      }
+    } else if (p.op == OP_AR2 && p.R > 1) {
+      // Collect the reduced tiles other owners broadcast into this rank's result
+      // buffer; copy them into the caller's tensor unless it aliases the buffer.
+      const int tiles = p.m_tiles * p.n_tiles;
+      bool ok = true;
+      for (int lin = blockIdx.x; ok && lin < tiles; lin += gridDim.x) {
+        if (lin % p.R == p.rank) continue;
+        if (ctid == 0)
+          ok = wait_flag_ge(p.peer_res_flags[p.rank] + lin, p.round, env, SITE_AR_RESULT, lin);
+        // all comm threads learn the outcome; also orders their loads after the acquire
+        if (ctid == 0) s_flags[1] = ok ? 1 : 0;
+        named_bar_sync(1, kCommThreads);
+        ok = s_flags[1] != 0;
+        named_bar_sync(1, kCommThreads);
+        if (!ok || p.res_is_c) continue;
+        int mt, nt;
+        raster_grouped(lin, p.m_tiles, p.n_tiles, mt, nt);
+        // raster_grouped is the inverse map used by tile_at for natural/strided order
+        const int rows = min(BM, p.M - mt * BM);
+        const int cols = min(BN, p.N - nt * BN);
+        const int v_per_row = cols >> 3;
+        for (int idx = ctid; idx < rows * v_per_row; idx += kCommThreads) {
+          const int r = idx / v_per_row;
+          const int v = idx - r * v_per_row;
+          const int64_t off = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
+          const uint4 val =
+              ld_global_cg_v4(reinterpret_cast<const uint8_t*>(p.peer_res[p.rank]) + off * 2);
+          st_global_v4(reinterpret_cast<uint8_t*>(p.c) +
+                           (static_cast<int64_t>(mt * BM + r) * p.ldc + nt * BN + v * 8) * 2,
+                       val);
+        }
+      }
+    }
+  }
+
+  // ==========================================================================
+  // teardown
+  // ==========================================================================
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TS::kTmemCols);
+  }
+}
+
+}  // namespace tdb

@@ -1,0 +1,30 @@
+// Small sm_100a kernels around the fused operators: SwiGLU, the cross-rank
+// ticket barrier, the bounded-wait self test, and spot verification of a GEMM result.
+#pragma once
+#include <cstdint>
+#include <vector>
+
+namespace tdb {
+
+// out[r, j] = silu(h[r, j]) * h[r, inter + j]   (gate and up halves stored side by side)
+void swiglu_launch(const void* h, void* out, int64_t rows, int64_t inter, int64_t ldh, bool bf16,
+                   void* stream);
+
+// Cross-rank barrier: writes `ticket` into slot [rank] of every rank's slot array, then
+// waits (bounded) until all R local slots reached the ticket.
+void barrier_launch(const std::vector<int64_t>& peer_slots, int rank, int R, uint32_t ticket,
+                    int64_t status_dev, int64_t abort_word, uint64_t timeout_ns, void* stream);
+
+// One thread waits for *flag >= ticket with the given limit; exercises timeout -> status.
+void wait_flag_test_launch(int64_t flag, uint32_t ticket, int64_t status_dev, int64_t abort_word,
+                           uint64_t timeout_ns, void* stream);
+
+void fill_u32_launch(uint32_t* p, int64_t n, uint32_t v, void* stream);
+
+// Recomputes `spots` pseudo-randomly chosen elements of every 128 x bn tile of
+// C = A @ B^T in fp32 and sets bad_tiles[tile] = 1 where |c - ref| > tol * (1 + |ref|).
+void spot_verify_launch(int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda,
+                        int64_t ldb, int64_t ldc, bool bf16, int spots, float tol,
+                        int64_t bad_tiles, int bn, void* stream);
+
+}  // namespace tdb

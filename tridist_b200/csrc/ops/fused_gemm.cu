@@ -1,0 +1,269 @@
+// Host side of the fused GEMM family: TMA descriptor encoding, plan objects
+// (one pre-built parameter block per workspace parity) and launches.
+#include "fused_gemm.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+
+#include "../gemm/fused_gemm.cuh"
+
+namespace tdb {
+
+static void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string("tridist_b200: ") + what + ": " + cudaGetErrorString(e));
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    check(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q),
+          "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    if (q != cudaDriverEntryPointSuccess || p == nullptr)
+      throw std::runtime_error("tridist_b200: cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Row-major [rows, cols] 16-bit matrix, box = 128 rows x 64 columns, 128-byte swizzle.
+static CUtensorMap make_tmap(const void* base, int64_t rows, int64_t cols, int64_t row_stride_elems,
+                             bool bf16) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
+    throw std::runtime_error("tridist_b200: TMA base address must be 16-byte aligned");
+  if ((row_stride_elems * 2) % 16 != 0)
+    throw std::runtime_error("tridist_b200: TMA row stride must be a multiple of 16 bytes");
+  CUtensorMap m;
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_stride_elems) * 2};
+  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           2, const_cast<void*>(base), gdim, gstride, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("tridist_b200: cuTensorMapEncodeTiled failed with code " +
+                             std::to_string(static_cast<int>(r)));
+  return m;
+}
+
+struct GemmPlan {
+  GemmParams prm[2];
+  int bn;
+  bool bf16;
+  int grid_x;
+  GemmParams* dev_params = nullptr;   // emulated multi-rank launches only
+};
+
+static std::mutex g_mu;
+static std::unordered_map<int64_t, GemmPlan*> g_plans;
+static int64_t g_next_plan = 1;
+static int64_t g_launches = 0;
+
+int64_t launch_count() { return g_launches; }
+void launch_count_add(int64_t n) { g_launches += n; }
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    check(cudaGetDevice(&dev), "cudaGetDevice");
+    check(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev), "SM count");
+  }
+  return n;
+}
+
+template <int BN, bool kBf16>
+static void set_attr_once() {
+  static bool done = false;
+  if (!done) {
+    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               TileShape<BN>::kSmemBytes),
+          "cudaFuncSetAttribute(smem)");
+    done = true;
+  }
+}
+
+int64_t gemm_plan_create(const GemmPlanDesc& d) {
+  if (d.R < 1 || d.R > kMaxRanks) throw std::runtime_error("tridist_b200: 1 <= R <= 8 required");
+  if (d.bn != 128 && d.bn != 256) throw std::runtime_error("tridist_b200: BN must be 128 or 256");
+  if (d.epi == EPI_SWIGLU && d.bn != 256)
+    throw std::runtime_error("tridist_b200: the SwiGLU epilogue needs BN = 256");
+  if (d.K % 8 != 0) throw std::runtime_error("tridist_b200: K must be a multiple of 8");
+  if (d.N % 8 != 0) throw std::runtime_error("tridist_b200: N must be a multiple of 8");
+  auto* plan = new GemmPlan();
+  plan->bn = d.bn;
+  plan->bf16 = d.bf16;
+  const int bn_out = (d.epi == EPI_SWIGLU) ? d.bn / 2 : d.bn;
+  for (int par = 0; par < 2; ++par) {
+    GemmParams& p = plan->prm[par];
+    std::memset(&p, 0, sizeof(p));
+    p.M = d.M; p.N = d.N; p.K = d.K;
+    p.m_tiles = (d.M + BM - 1) / BM;
+    p.n_tiles = (d.N + bn_out - 1) / bn_out;
+    p.k_blocks = (d.K + BK - 1) / BK;
+    p.rank = d.rank; p.R = d.R;
+    p.op = d.op; p.epi = d.epi; p.sched = d.sched;
+    p.m_per_rank = d.m_per_rank > 0 ? d.m_per_rank : d.M;
+    p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? p.m_tiles / d.R : p.m_tiles;
+    if (d.sched == SCHED_SEGMENT && (p.m_tiles % d.R != 0 || p.m_per_rank % BM != 0))
+      throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
+    for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
+    p.order_table = reinterpret_cast<const int32_t*>(d.order_table);
+    p.tile_list = reinterpret_cast<const int32_t*>(d.tile_list);
+    p.list_len = d.list_len;
+    p.swiglu_up_row0 = d.swiglu_up_row0;
+    p.is_bf16 = d.bf16 ? 1 : 0;
+    p.c = reinterpret_cast<void*>(d.c);
+    p.ldc = d.ldc;
+    p.tma_a = make_tmap(reinterpret_cast<void*>(d.a), d.a_rows, d.K, d.lda, d.bf16);
+    p.tma_b = make_tmap(reinterpret_cast<void*>(d.b), d.b_rows, d.K, d.ldb, d.bf16);
+    p.tma_a_ws = p.tma_a;
+    p.a_local = reinterpret_cast<const void*>(d.a);
+    p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;
+    p.n_chunks = d.n_chunks > 0 ? d.n_chunks : 1;
+    p.push_parts = d.push_parts > 0 ? d.push_parts : 1;
+    p.skip_comm = d.skip_comm;
+    p.ag_counters = reinterpret_cast<uint32_t*>(d.ag_counters);
+    p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
+    p.slot_stride = d.slot_stride;
+    p.res_is_c = d.res_is_c;
+    for (int r = 0; r < d.R; ++r) {
+      p.peer_ws[r] = reinterpret_cast<void*>(d.peer_ws[par][r]);
+      p.peer_ag_flags[r] = reinterpret_cast<uint32_t*>(d.peer_ag_flags[r]);
+      p.peer_slots[r] = reinterpret_cast<void*>(d.peer_slots[par][r]);
+      p.peer_tile_flags[r] = reinterpret_cast<uint32_t*>(d.peer_tile_flags[r]);
+      p.peer_res[r] = reinterpret_cast<void*>(d.peer_res[par][r]);
+      p.peer_res_flags[r] = reinterpret_cast<uint32_t*>(d.peer_res_flags[r]);
+    }
+    if (d.op == OP_AG && d.R > 1) {
+      if (((static_cast<int64_t>(p.chunk_rows) * d.K * 2) / p.push_parts) % 16 != 0)
+        throw std::runtime_error("tridist_b200: AG push part size must be a multiple of 16 bytes");
+      p.tma_a_ws = make_tmap(p.peer_ws[d.rank], d.M, d.K, d.K, d.bf16);
+    }
+    p.env.status = reinterpret_cast<StatusBlock*>(d.status_dev);
+    p.env.abort_word = reinterpret_cast<uint32_t*>(d.abort_word);
+    p.env.timeout_ns = d.timeout_ns;
+    p.env.rank = static_cast<uint32_t>(d.rank);
+  }
+  {
+    const GemmParams& p = plan->prm[0];
+    int positions = p.m_tiles * p.n_tiles;
+    if (p.sched == SCHED_STRIDED) positions = ((positions + p.R - 1) / p.R) * p.R;
+    if (p.sched == SCHED_LIST) positions = p.list_len;
+    int g = d.max_ctas > 0 ? d.max_ctas : num_sms();
+    if (g > num_sms()) g = num_sms();
+    plan->grid_x = positions < g ? positions : g;
+    if (plan->grid_x < 1) plan->grid_x = 1;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  const int64_t id = g_next_plan++;
+  g_plans[id] = plan;
+  return id;
+}
+
+void gemm_plan_destroy(int64_t id) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_plans.find(id);
+  if (it == g_plans.end()) return;
+  if (it->second->dev_params) cudaFree(it->second->dev_params);
+  delete it->second;
+  g_plans.erase(it);
+}
+
+static GemmPlan* find_plan(int64_t id) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_plans.find(id);
+  if (it == g_plans.end()) throw std::runtime_error("tridist_b200: unknown GEMM plan");
+  return it->second;
+}
+
+template <int BN, bool kBf16>
+static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
+  set_attr_once<BN, kBf16>();
+  fused_gemm_kernel<BN, kBf16>
+      <<<dim3(grid_x, 1, 1), dim3(kThreads, 1, 1), TileShape<BN>::kSmemBytes, stream>>>(p, nullptr);
+  check(cudaGetLastError(), "fused_gemm_kernel launch");
+}
+
+void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm,
+                      void* stream_) {
+  GemmPlan* plan = find_plan(id);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  GemmParams& p = plan->prm[parity & 1];
+  p.round = round;
+  p.order_table = reinterpret_cast<const int32_t*>(order_table);
+  p.skip_comm = skip_comm;
+  if (plan->bn == 256) {
+    if (plan->bf16) launch_one<256, true>(p, plan->grid_x, stream);
+    else launch_one<256, false>(p, plan->grid_x, stream);
+  } else {
+    if (plan->bf16) launch_one<128, true>(p, plan->grid_x, stream);
+    else launch_one<128, false>(p, plan->grid_x, stream);
+  }
+  ++g_launches;
+}
+
+template <int BN, bool kBf16>
+static void launch_emulated(const GemmParams* dev, int grid_x, int vranks, cudaStream_t stream) {
+  set_attr_once<BN, kBf16>();
+  GemmParams dummy;
+  std::memset(&dummy, 0, sizeof(dummy));
+  void* args[2] = {&dummy, &dev};
+  // Cooperative launch: the runtime refuses the launch unless every CTA of
+  // every emulated rank can be resident at once, which the cross-rank waits need.
+  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16>),
+                                    dim3(grid_x, vranks, 1), dim3(kThreads, 1, 1), args,
+                                    TileShape<BN>::kSmemBytes, stream),
+        "fused_gemm_kernel cooperative launch");
+}
+
+void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round, int parity,
+                                int skip_comm, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int vr = static_cast<int>(ids.size());
+  if (vr < 1 || vr > kMaxRanks) throw std::runtime_error("tridist_b200: bad emulated rank count");
+  GemmPlan* first = find_plan(ids[0]);
+  std::vector<GemmParams> host(vr);
+  int grid_x = num_sms() / vr;
+  for (int i = 0; i < vr; ++i) {
+    GemmPlan* pl = find_plan(ids[i]);
+    if (pl->bn != first->bn || pl->bf16 != first->bf16)
+      throw std::runtime_error("tridist_b200: emulated ranks must share the kernel variant");
+    host[i] = pl->prm[parity & 1];
+    host[i].round = round;
+    host[i].skip_comm = skip_comm;
+    if (pl->grid_x < grid_x) grid_x = pl->grid_x;
+  }
+  if (!first->dev_params)
+    check(cudaMalloc(&first->dev_params, sizeof(GemmParams) * kMaxRanks), "cudaMalloc(params)");
+  check(cudaMemcpyAsync(first->dev_params, host.data(), sizeof(GemmParams) * vr,
+                        cudaMemcpyHostToDevice, stream),
+        "cudaMemcpyAsync(params)");
+  check(cudaStreamSynchronize(stream), "cudaStreamSynchronize(params)");
+  if (first->bn == 256) {
+    if (first->bf16) launch_emulated<256, true>(first->dev_params, grid_x, vr, stream);
+    else launch_emulated<256, false>(first->dev_params, grid_x, vr, stream);
+  } else {
+    if (first->bf16) launch_emulated<128, true>(first->dev_params, grid_x, vr, stream);
+    else launch_emulated<128, false>(first->dev_params, grid_x, vr, stream);
+  }
+  ++g_launches;
+}
+
+}  // namespace tdb

@@ -1,0 +1,60 @@
+// Plain-C++ interface of the fused GEMM family (no torch / pybind types here).
+#pragma once
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+namespace tdb {
+
+// All pointers are device addresses passed as integers. Arrays indexed [parity][rank]
+// hold the two generations of a double-buffered symmetric buffer: a call with an
+// odd round uses parity 1. Because a rank can only enter round n+1 after every
+// peer finished round n-1, writes of round n+1 never touch memory a peer still reads.
+struct GemmPlanDesc {
+  int op = 0, epi = 0, sched = 0;
+  int bn = 256;
+  bool bf16 = false;
+  int rank = 0, R = 1;
+  int M = 0, N = 0, K = 0;
+  int64_t a = 0, a_rows = 0, lda = 0;
+  int64_t b = 0, b_rows = 0, ldb = 0;
+  int64_t c = 0, ldc = 0;
+  int m_per_rank = 0;
+  int seg_order[8] = {0, 1, 2, 3, 4, 5, 6, 7};
+  int64_t order_table = 0;
+  int64_t tile_list = 0;
+  int list_len = 0;
+  int swiglu_up_row0 = 0;
+  int max_ctas = 0;
+  // all-gather
+  int64_t peer_ws[2][8] = {};
+  int64_t peer_ag_flags[8] = {};
+  int64_t ag_counters = 0;
+  int64_t arrival_ns = 0;
+  int chunk_rows = 0, n_chunks = 0, push_parts = 0, skip_comm = 0;
+  // reduce-scatter / all-reduce
+  int64_t peer_slots[2][8] = {};
+  int64_t peer_tile_flags[8] = {};
+  int64_t slot_stride = 0;
+  int64_t peer_res[2][8] = {};
+  int64_t peer_res_flags[8] = {};
+  int res_is_c = 0;
+  // failure reporting
+  int64_t status_dev = 0;
+  int64_t abort_word = 0;
+  uint64_t timeout_ns = 2000000000ull;
+};
+
+int64_t gemm_plan_create(const GemmPlanDesc& d);
+void gemm_plan_destroy(int64_t id);
+// `order_table`: optional device int32[R] overriding the segment order for this call.
+void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm,
+                      void* stream);
+// Runs several ranks' plans as ONE cooperative kernel on one GPU (grid.y = rank).
+void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round, int parity,
+                                int skip_comm, void* stream);
+
+int64_t launch_count();
+void launch_count_add(int64_t n);
+
+}  // namespace tdb

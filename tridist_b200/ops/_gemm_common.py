@@ -1,0 +1,151 @@
+"""Shared host logic of the fused GEMM operators: plan construction and caching.
+
+A *plan* is a pre-built kernel parameter block (TMA descriptors, peer pointers,
+tile order) for one (context, tensors, shapes) combination; launching a cached
+plan costs one kernel launch and no descriptor encoding.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, List, Optional
+
+import torch
+
+from ..parallel.runtime import native
+from ..utils.config import env_int
+
+OP_PLAIN, OP_AG, OP_RS, OP_AR1, OP_AR2 = 0, 1, 2, 3, 4
+EPI_STORE, EPI_SWIGLU = 0, 1
+SCHED_NATURAL, SCHED_SEGMENT, SCHED_STRIDED, SCHED_LIST = 0, 1, 2, 3
+BM = 128
+NUM_SMS_HINT = 148
+
+
+def is_bf16(dtype: torch.dtype) -> bool:
+    if dtype == torch.bfloat16:
+        return True
+    if dtype == torch.float16:
+        return False
+    raise TypeError(f"tridist_b200: fused GEMM kernels support fp16 and bf16, got {dtype}")
+
+
+def choose_bn(M: int, N: int, swiglu: bool = False) -> int:
+    """Output-tile width: 256 unless that leaves most SMs without a tile."""
+    if swiglu:
+        return 256       # gate and up halves are two 128-row TMA boxes of one 256-wide tile
+    forced = env_int("TRIDIST_FORCE_BN", 0)
+    if forced in (128, 256):
+        return forced
+    m_tiles = (M + BM - 1) // BM
+    width = 128 if swiglu else 256           # output columns covered by a BN=256 tile
+    tiles256 = m_tiles * ((N + width - 1) // width)
+    return 256 if tiles256 >= NUM_SMS_HINT - 28 else 128
+
+
+def rotation_order(rank: int, R: int, step: int, own_last: bool) -> List[int]:
+    """Segment visiting order.
+
+    own_last=False (all-gather): own rows first, then rank-1, rank-2, ... — the
+    order in which shards arrive when every rank pushes to rank+1 first.
+    own_last=True (reduce-scatter / all-reduce): rank+1 first, own rows last, so
+    that every owner receives its first partial tiles as early as possible.
+    """
+    if own_last:
+        return [(rank + 1 + i) % R for i in range(R)]
+    return [(rank - i * step) % R for i in range(R)]
+
+
+class PlanCache:
+    def __init__(self, capacity: int = 64):
+        self.capacity = capacity
+        self._d: "OrderedDict[tuple, int]" = OrderedDict()
+
+    def get(self, key: tuple, make) -> int:
+        pid = self._d.get(key)
+        if pid is not None:
+            self._d.move_to_end(key)
+            return pid
+        pid = make()
+        self._d[key] = pid
+        if len(self._d) > self.capacity:
+            _, old = self._d.popitem(last=False)
+            native().gemm_plan_destroy(old)
+        return pid
+
+    def clear(self) -> None:
+        C = native()
+        for pid in self._d.values():
+            C.gemm_plan_destroy(pid)
+        self._d.clear()
+
+
+def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr: int, ldc: int,
+              M: int, N: int, K: int, bn: int, op: int) -> Dict:
+    assert a.stride(1) == 1 and b.stride(1) == 1, "operands must be row-major with unit inner stride"
+    d = dict(op=op, epi=EPI_STORE, sched=SCHED_NATURAL, bn=bn, bf16=is_bf16(a.dtype), rank=rank, R=R,
+             M=M, N=N, K=K, a=a.data_ptr(), a_rows=a.shape[0], lda=a.stride(0),
+             b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
+             status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
+             max_ctas=env_int("TRIDIST_MAX_CTAS", 0))
+    return d
+
+
+# ---------------------------------------------------------------------------
+# Plain single-GPU GEMM (the R = 1 degenerate of every fused operator and the
+# building block of the tile-config sweeps)
+# ---------------------------------------------------------------------------
+_plain_cache = PlanCache(128)
+_plain_world = None
+
+
+class _PlainWorld:
+    """Minimal status plumbing for GEMMs launched outside any context."""
+
+    def __init__(self):
+        C = native()
+        self.status_host, self.status_dev = C.status_alloc()
+        self._abort = torch.zeros(64, dtype=torch.int32, device="cuda")
+        self.abort_word = self._abort.data_ptr()
+        self.timeout_ns = env_int("TRIDIST_WAIT_TIMEOUT_MS", 4000) * 1_000_000
+
+
+def plain_world():
+    global _plain_world
+    if _plain_world is None:
+        _plain_world = _PlainWorld()
+    return _plain_world
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+            bn: Optional[int] = None, swiglu: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """``out = a @ b.T`` on the hand-written tcgen05 kernel (fp32 accumulate).
+
+    With ``swiglu=True`` b holds ``[gate; up]`` row blocks (2*I rows) and the
+    result is ``silu(a @ gate.T) * (a @ up.T)`` of shape [M, I], computed in the
+    GEMM epilogue.
+    """
+    assert a.is_cuda and b.is_cuda and a.dtype == b.dtype
+    M, K = a.shape
+    n_rows = b.shape[0]
+    N = n_rows // 2 if swiglu else n_rows
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    assert out.stride(1) == 1
+    if bn is None:
+        bn = choose_bn(M, N, swiglu)
+    w = plain_world()
+    key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+           out.stride(0), bn, swiglu, a.dtype, max_ctas)
+
+    def make():
+        d = base_desc(w, 0, 1, a, b, out.data_ptr(), out.stride(0), M, N, K, bn, OP_PLAIN)
+        if swiglu:
+            d["epi"] = EPI_SWIGLU
+            d["swiglu_up_row0"] = N
+        if max_ctas:
+            d["max_ctas"] = max_ctas
+        return native().gemm_plan_create(d)
+
+    pid = _plain_cache.get(key, make)
+    native().gemm_plan_launch(pid, 1, 0, 0, 0)
+    return out

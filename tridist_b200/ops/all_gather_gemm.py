@@ -1,0 +1,217 @@
+"""All-gather + GEMM:  C = allgather_M(A) @ B^T   (tensor/sequence parallel input side).
+
+Public API and semantics follow the reference
+(triton_dist/kernels/dcu/all_gather_gemm.py:317-497):
+
+* ``create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
+  num_ranks, mpi, comm, M_PER_CHUNK=1024, ag_stream=None, gemm_stream=None)``
+* ``ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False)`` with ``a[M_pr, K]`` this
+  rank's shard, ``b[N_pr, K]`` this rank's weight, ``c[M, N_pr]`` caller-allocated;
+  row block s of C comes from rank s's shard.
+* ``ag_gemm_intra_node(a, b, transe_b, ctx)`` allocates C.
+
+What differs is the mechanism: one persistent sm_100a kernel per call. Its
+communication warps push the local shard into every peer's workspace with
+16-byte stores over NVLink and raise a per-(source, chunk) ticket; its TMA warp
+waits for the ticket of a remote row block, then loads it from the local
+workspace; tcgen05 tiles run own rows first, then sources in arrival order.
+There is no host-side synchronisation and no global barrier: the workspace is
+double-buffered by call parity.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from ..parallel import cpu_backend
+from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
+                                native)
+from ._gemm_common import (BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
+                           base_desc, choose_bn, rotation_order)
+
+_CONSUMER_BLOCK_M = 128
+_CONSUMER_BLOCK_N = 128
+
+
+@dataclass
+class AllGatherGEMMTensorParallelContext:
+    rank: int
+    num_ranks: int
+    max_M: int
+    K: int
+    input_dtype: torch.dtype
+    output_dtype: torch.dtype
+    M_PER_CHUNK: int
+    world: object
+    ws: Optional[SymmBuffer] = None          # [2][max_M, K] gathered A, double-buffered
+    flags: Optional[SymmBuffer] = None       # u32 [R, max_chunks] tickets, indexed by source
+    counters: Optional[torch.Tensor] = None  # local part counters of the push
+    arrival_ns: Optional[torch.Tensor] = None  # int64 [R] first-seen arrival stamps (observer)
+    flag_round: int = 0
+    ag_stream: Optional[torch.cuda.Stream] = None
+    gemm_stream: Optional[torch.cuda.Stream] = None
+    plans: PlanCache = field(default_factory=PlanCache)
+    observe: bool = False
+    order_override: Optional[List[int]] = None
+    last_gathered: Optional[torch.Tensor] = None   # CPU backend: last gathered A (skip_comm)
+
+    @property
+    def max_chunks(self) -> int:
+        return max(1, (self.max_M // self.num_ranks) // self.M_PER_CHUNK)
+
+    @property
+    def ws_ptr(self) -> int:
+        return self.ws.local_ptr
+
+    def workspace(self, parity: int, M: int) -> torch.Tensor:
+        """This rank's gathered A of the given parity as a [M, K] tensor."""
+        off = parity * self.max_M * self.K * 2
+        return self.ws.tensor(self.input_dtype, (M, self.K), off, rank=self.rank)
+
+
+def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank, num_ranks, mpi=None,
+                                      comm=None, M_PER_CHUNK=1024, ag_stream=None, gemm_stream=None,
+                                      world=None):
+    """Collective. Allocates the symmetric workspace and ticket planes.
+
+    ``mpi`` is accepted for signature compatibility and ignored; ``comm`` may be
+    a ``torch.distributed`` process group.
+    """
+    assert max_M % num_ranks == 0, "max_M must be divisible by num_ranks"
+    m_pr = max_M // num_ranks
+    M_PER_CHUNK = min(M_PER_CHUNK, m_pr)
+    assert m_pr % M_PER_CHUNK == 0, "rows per rank must be a multiple of M_PER_CHUNK"
+    assert M_PER_CHUNK % 128 == 0, "M_PER_CHUNK must be a multiple of 128"
+    if world is None:
+        world = default_world() or init_runtime(rank, num_ranks, comm)
+    ctx = AllGatherGEMMTensorParallelContext(rank=rank, num_ranks=num_ranks, max_M=max_M, K=K,
+                                             input_dtype=input_dtype, output_dtype=output_dtype,
+                                             M_PER_CHUNK=M_PER_CHUNK, world=world,
+                                             ag_stream=ag_stream, gemm_stream=gemm_stream)
+    if isinstance(world, CpuWorld):
+        return ctx
+    assert input_dtype == output_dtype, "the fused kernel emits the input dtype"
+    ctx.ws = world.alloc(2 * max_M * K * 2)
+    ctx.flags = world.alloc(num_ranks * ctx.max_chunks * 4)
+    if isinstance(world, EmulatedWorld):
+        ctx.ws = world.view(ctx.ws, rank)
+        ctx.flags = world.view(ctx.flags, rank)
+    ctx.counters = torch.zeros(num_ranks * ctx.max_chunks, dtype=torch.int32, device="cuda")
+    ctx.arrival_ns = torch.zeros(num_ranks, dtype=torch.int64, device="cuda")
+    world.host_barrier()
+    return ctx
+
+
+def _push_parts(chunk_rows: int) -> int:
+    parts = 64
+    while parts > 1 and chunk_rows % parts != 0:
+        parts //= 2
+    return parts
+
+
+def _plan(ctx, a, b, c, swiglu=False):
+    R, rank = ctx.num_ranks, ctx.rank
+    m_pr, K = a.shape
+    M = m_pr * R
+    n_rows = b.shape[0]
+    N = n_rows // 2 if swiglu else n_rows
+    bn = choose_bn(M, N, swiglu)
+    order = ctx.order_override or rotation_order(rank, R, 1, own_last=False)
+    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, c.stride(0), a.dtype, swiglu, bn,
+           tuple(order))
+
+    def make():
+        d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, OP_AG)
+        d["a_rows"] = m_pr
+        d["m_per_rank"] = m_pr
+        d["sched"] = SCHED_SEGMENT if (m_pr % BM == 0) else SCHED_NATURAL
+        d["seg_order"] = order
+        if swiglu:
+            d["epi"] = EPI_SWIGLU
+            d["swiglu_up_row0"] = N
+        if R > 1:
+            half = ctx.max_M * K * 2
+            d["peer_ws"] = [ctx.ws.ptrs(0), ctx.ws.ptrs(half)]
+            d["peer_ag_flags"] = ctx.flags.ptrs()
+            d["ag_counters"] = ctx.counters.data_ptr()
+            d["arrival_ns"] = ctx.arrival_ns.data_ptr() if ctx.observe else 0
+            chunk = min(ctx.M_PER_CHUNK, m_pr)
+            d["chunk_rows"] = chunk
+            d["n_chunks"] = m_pr // chunk
+            d["push_parts"] = _push_parts(chunk)
+        return native().gemm_plan_create(d)
+
+    return ctx.plans.get(key, make)
+
+
+def _check_args(a, b, c, ctx):
+    m_pr, K = a.shape
+    M = m_pr * ctx.num_ranks
+    assert K == ctx.K and M <= ctx.max_M, "shape exceeds the context"
+    assert a.dtype == ctx.input_dtype and b.dtype == ctx.input_dtype
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) == K, "a must be a contiguous [M_pr, K] shard"
+    assert M % _CONSUMER_BLOCK_M == 0 and b.shape[0] % _CONSUMER_BLOCK_N == 0
+    assert K % 16 == 0
+    chunk = min(ctx.M_PER_CHUNK, m_pr)
+    assert m_pr % chunk == 0
+    assert c.shape[0] == M and c.stride(1) == 1
+
+
+def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[torch.Tensor] = None,
+                          fuse_swiglu: bool = False):
+    """``c[M, N_pr] = allgather_M(a) @ b.T``.
+
+    ``skip_comm=True`` is the GEMM-only decomposition mode: the kernel multiplies
+    the workspace left by the last full call and pushes nothing.
+    ``order_table`` (device int32[R]) overrides the source visiting order for this
+    call (skew-aware scheduling). ``fuse_swiglu`` treats b as ``[gate; up]`` and
+    writes ``silu(gate) * up`` (c has N_pr/2 columns).
+    """
+    if isinstance(ctx.world, CpuWorld):
+        return cpu_backend.ag_gemm(a, b, c, ctx, skip_comm, fuse_swiglu)
+    _check_args(a, b, c, ctx)
+    if not skip_comm:
+        ctx.flag_round += 1
+    if ctx.flag_round == 0:
+        raise RuntimeError("skip_comm=True needs a full call on this context first")
+    if ctx.observe and not skip_comm:
+        ctx.arrival_ns.fill_(torch.iinfo(torch.int64).max)
+    pid = _plan(ctx, a, b, c, fuse_swiglu)
+    native().gemm_plan_launch(pid, ctx.flag_round, ctx.flag_round & 1,
+                              order_table.data_ptr() if order_table is not None else 0,
+                              1 if skip_comm else 0)
+    return c
+
+
+def ag_gemm_intra_node(a, b, transe_b, ctx):
+    """Allocating wrapper (reference signature; ``transe_b=True`` is not supported there either)."""
+    if transe_b:
+        raise NotImplementedError("transe_b=True is not implemented")
+    M = a.shape[0] * ctx.num_ranks
+    c = torch.empty((M, b.shape[0]), dtype=ctx.output_dtype, device=a.device)
+    return ag_gemm_intra_node_op(a, b, c, ctx)
+
+
+def ag_gemm_emulated(ctxs, a_list, b_list, c_list, skip_comm=False, fuse_swiglu=False):
+    """All ranks of an ``EmulatedWorld`` in one cooperative launch (single-GPU protocol test)."""
+    for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list):
+        _check_args(a, b, c, ctx)
+        if not skip_comm:
+            ctx.flag_round += 1
+    pids = [_plan(ctx, a, b, c, fuse_swiglu) for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list)]
+    rnd = ctxs[0].flag_round
+    native().gemm_plans_launch_emulated(pids, rnd, rnd & 1, 1 if skip_comm else 0)
+    return c_list
+
+
+def finalize_ag_gemm_context(ctx) -> None:
+    """Collective: release the symmetric buffers of the context."""
+    if ctx.ws is None:
+        return
+    ctx.plans.clear()
+    if not isinstance(ctx.world, EmulatedWorld):
+        ctx.world.free(ctx.ws)
+        ctx.world.free(ctx.flags)
+    ctx.ws = ctx.flags = None

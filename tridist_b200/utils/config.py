@@ -1,0 +1,46 @@
+"""Environment-variable knobs.
+
+The reference configures itself through constructor keywords, module constants
+and environment variables (``TD_PUSH_STREAMS``, ``RD_WAIT_MODE``, ``I1_VERIFY`` ...,
+triton_dist/kernels/dcu/common_ops.py:92-97, ag_tr_pred.py:85-170).  The knobs
+that still mean something on B200 are read here, under the ``TRIDIST_`` prefix.
+
+TRIDIST_WAIT_TIMEOUT_MS   limit of every in-kernel wait (default 4000)
+TRIDIST_MAX_CTAS          cap on the persistent grid of the fused GEMM kernels
+TRIDIST_FORCE_BN          128 or 256: override the output-tile width heuristic
+TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot"
+TRIDIST_AR_ONE_SHOT_BYTES size threshold (bytes of one rank's partial) below which
+                          the one-shot all-reduce is used (default 4 MiB)
+TRIDIST_VERIFY            1: spot-verify fused AG+GEMM results and repair flagged tiles
+TRIDIST_VERIFY_SPOTS      elements recomputed per tile (default 4)
+TRIDIST_VERIFY_TOL        relative tolerance of the spot check (default 2e-2)
+"""
+from __future__ import annotations
+
+import os
+
+
+def env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return int(v)
+
+
+def env_float(name: str, default: float) -> float:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return float(v)
+
+
+def env_str(name: str, default: str) -> str:
+    v = os.environ.get(name)
+    return default if v is None or v == "" else v
+
+
+def env_flag(name: str, default: bool = False) -> bool:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return v.lower() not in ("0", "false", "no", "off")
