@@ -1,0 +1,287 @@
+"""Single-GPU tests of the sm_100a kernels.
+
+Numerics are compared against a plain fp32 PyTorch reference of the same op.
+The cross-rank protocols (tickets, peer slots, segment tables) are exercised on
+one GPU by running R virtual ranks inside one cooperative launch
+(``EmulatedWorld``); real multi-process runs live in test_gpu_multi.py.
+"""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _world1():
+    from tridist_b200.parallel.runtime import ProcessWorld
+    global _W1
+    try:
+        return _W1
+    except NameError:
+        _W1 = ProcessWorld(0, 1)
+        return _W1
+
+
+def _loaded_native():
+    from tridist_b200.parallel.runtime import native
+    C = native()
+    assert C.__file__.endswith("_C.so")
+    return C
+
+
+TOL = 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape,bn", [((128, 256, 64), 256), ((256, 128, 192), 128), ((384, 640, 1000), None),
+                                      ((1024, 2048, 512), None), ((192, 384, 520), 256)])
+def test_plain_gemm(shape, bn, dtype):
+    from tridist_b200.ops._gemm_common import gemm_nt
+    _loaded_native()
+    M, N, K = shape
+    torch.manual_seed(1)
+    a = (torch.randn(M, K, device="cuda") * 0.05).to(dtype)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(dtype)
+    before = _loaded_native().launch_count()
+    out = gemm_nt(a, b, bn=bn)
+    torch.cuda.synchronize()
+    assert _loaded_native().launch_count() == before + 1
+    ref = a.float() @ b.float().t()
+    assert (out.float() - ref).abs().max().item() < TOL
+
+
+def test_gemm_swiglu_epilogue_and_kernel():
+    from tridist_b200.ops import swiglu
+    from tridist_b200.ops._gemm_common import gemm_nt
+    torch.manual_seed(2)
+    M, I, K = 512, 640, 384
+    a = (torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda") * 0.1).to(torch.bfloat16)
+    h = a.float() @ w.float().t()
+    ref = F.silu(h[:, :I]) * h[:, I:]
+    fused = gemm_nt(a, w, swiglu=True)
+    two_step = swiglu(gemm_nt(a, w))
+    torch.cuda.synchronize()
+    assert (fused.float() - ref).abs().max().item() < TOL
+    assert (two_step.float() - ref).abs().max().item() < 3e-2   # h rounded to bf16 first
+    # stand-alone kernel against torch on the same 16-bit input
+    hh = (torch.randn(300, 2 * 264, device="cuda")).to(torch.float16)
+    got = swiglu(hh)
+    exp = (F.silu(hh[:, :264].float()) * hh[:, 264:].float())
+    assert (got.float() - exp).abs().max().item() < 1e-2
+
+
+def test_public_api_single_rank():
+    """R = 1 degenerates: every op collapses to the local GEMM / permutation."""
+    from tridist_b200.ops import (ag_gemm_intra_node, create_ag_gemm_intra_node_context,
+                                  create_gemm_ar_intra_node_context, create_gemm_rs_intra_node_context,
+                                  create_moe_a2a_intra_node_context, gemm_ar_intra_node, gemm_rs_intra_node,
+                                  moe_combine_intra_node_op, moe_dispatch_intra_node_op)
+    from tridist_b200.utils.testing import fake_expert, moe_inputs
+    w = _world1()
+    torch.manual_seed(3)
+    dt = torch.float16
+    M, N, K = 512, 768, 256
+    a = (torch.randn(M, K, device="cuda") * 0.05).to(dt)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(dt)
+    ref = a.float() @ b.float().t()
+    ctx = create_ag_gemm_intra_node_context(M, K, dt, dt, 0, 1, M_PER_CHUNK=256, world=w)
+    assert (ag_gemm_intra_node(a, b, False, ctx).float() - ref).abs().max().item() < TOL
+    rs = create_gemm_rs_intra_node_context(M, N, dt, 0, 1, world=w)
+    assert (gemm_rs_intra_node(a, b, rs).float() - ref).abs().max().item() < TOL
+    ar = create_gemm_ar_intra_node_context(M, N, dt, dt, 0, 1, world=w)
+    assert (gemm_ar_intra_node(a, b, ar).float() - ref).abs().max().item() < TOL
+    E, H, topk, T = 8, 256, 2, 96
+    moe = create_moe_a2a_intra_node_context(E, H, dt, T, topk, 0, 1, world=w)
+    tokens, idx, wts = [x.cuda() for x in moe_inputs(0, T, H, E, topk, 0, dt)]
+    n = int(moe_dispatch_intra_node_op(tokens, idx, moe).item())
+    assert n == T * topk
+    sc = moe.scatter_idx[:T].long()
+    assert sorted(sc.flatten().tolist()) == list(range(n))          # bijection onto rows
+    assert torch.equal(moe.recv[sc[:, 0]], tokens)                  # content
+    moe.out[:n] = fake_expert(moe.recv[:n])
+    out = torch.empty_like(tokens)
+    moe_combine_intra_node_op(moe, idx, out, wts)
+    exp = (wts.unsqueeze(-1) * (tokens.float().unsqueeze(1) * 2 + (sc % 5).float().unsqueeze(-1))).sum(1)
+    torch.cuda.synchronize()
+    w.check()
+    assert (out.float() - exp).abs().max().item() < 2e-2
+
+
+def _emu(R):
+    from tridist_b200.parallel.runtime import EmulatedWorld
+    return EmulatedWorld(R)
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_ag_gemm_emulated(R):
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    from tridist_b200.utils.testing import ag_inputs
+    w = _emu(R)
+    dt = torch.bfloat16
+    m_pr, K, n_pr = 256, 512, 384
+    ctxs = [create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, r, R, M_PER_CHUNK=128, world=w) for r in range(R)]
+    for it in range(3):                                   # fresh data every round, both parities
+        ins = [ag_inputs(r, R, m_pr, K, n_pr, it, dt, 0.05) for r in range(R)]
+        a_list = [ins[r][0][r].cuda() for r in range(R)]
+        b_list = [ins[r][1].cuda() for r in range(R)]
+        c_list = [torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda") for _ in range(R)]
+        ag_gemm_emulated(ctxs, a_list, b_list, c_list)
+        torch.cuda.synchronize()
+        w.check()
+        full = torch.cat([x.float() for x in a_list], 0)
+        for r in range(R):
+            ref = full @ b_list[r].float().t()
+            assert (c_list[r].float() - ref).abs().max().item() < TOL, f"round {it} rank {r}"
+            ws = ctxs[r].workspace(ctxs[r].flag_round & 1, m_pr * R)
+            for s in range(R):
+                if s != r:                                # pushed shards landed bit-exactly
+                    assert torch.equal(ws[s * m_pr:(s + 1) * m_pr], a_list[s])
+    # GEMM-only decomposition on the last workspace gives the same result
+    c2 = [torch.empty_like(c) for c in c_list]
+    ag_gemm_emulated(ctxs, a_list, b_list, c2, skip_comm=True)
+    torch.cuda.synchronize()
+    for r in range(R):
+        assert torch.equal(c2[r], c_list[r])
+
+
+@pytest.mark.parametrize("R,M", [(2, 512), (4, 512), (4, 256)])
+def test_gemm_rs_emulated(R, M):
+    from tridist_b200.ops.gemm_reduce_scatter import create_gemm_rs_intra_node_context, gemm_rs_emulated
+    from tridist_b200.utils.testing import ks_inputs
+    w = _emu(R)
+    dt = torch.float16
+    N, kl = 384, 256
+    ctxs = [create_gemm_rs_intra_node_context(M, N, dt, r, R, world=w) for r in range(R)]
+    for it in range(3):
+        a_all, b_all = ks_inputs(R, M, N, kl, it, dt, 0.05)
+        a_all = [x.cuda() for x in a_all]
+        b_all = [x.cuda() for x in b_all]
+        outs = gemm_rs_emulated(ctxs, a_all, b_all)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
+        m_pr = M // R
+        for r in range(R):
+            err = (outs[r].float() - ref[r * m_pr:(r + 1) * m_pr]).abs().max().item()
+            assert err < TOL, f"round {it} rank {r}: {err}"
+
+
+@pytest.mark.parametrize("mode", ["one_shot", "two_shot"])
+@pytest.mark.parametrize("R,M", [(2, 256), (4, 192)])
+def test_gemm_ar_emulated(R, M, mode):
+    from tridist_b200.ops.gemm_allreduce import create_gemm_ar_intra_node_context, gemm_ar_emulated
+    from tridist_b200.utils.testing import ks_inputs
+    w = _emu(R)
+    dt = torch.bfloat16
+    N, kl = 640, 192
+    ctxs = [create_gemm_ar_intra_node_context(256, N, dt, dt, r, R, M_PER_CHUNK=64, world=w) for r in range(R)]
+    for it in range(3):
+        a_all, b_all = ks_inputs(R, M, N, kl, it, dt, 0.05)
+        a_all = [x.cuda() for x in a_all]
+        b_all = [x.cuda() for x in b_all]
+        use_symm = (mode == "two_shot" and it == 2)
+        c_list = [ctxs[r].symm_output(M) if use_symm else torch.empty(M, N, dtype=dt, device="cuda")
+                  for r in range(R)]
+        gemm_ar_emulated(ctxs, a_all, b_all, c_list, mode=mode)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
+        for r in range(R):
+            err = (c_list[r].float() - ref).abs().max().item()
+            assert err < 2e-2, f"round {it} rank {r}: {err}"
+            assert torch.equal(c_list[r], c_list[0]), "all-reduce result must be bit-identical on all ranks"
+
+
+@pytest.mark.parametrize("zipf", [0.0, 1.2])
+def test_moe_emulated(zipf):
+    from tridist_b200.ops.moe_a2a import (create_moe_a2a_intra_node_context, moe_combine_emulated,
+                                          moe_dispatch_emulated)
+    from tridist_b200.utils.testing import fake_expert, moe_inputs
+    R, E, H, topk, T = 4, 16, 512, 4, 200
+    w = _emu(R)
+    dt = torch.float16
+    ctxs = [create_moe_a2a_intra_node_context(E, H, dt, T, topk, r, R, world=w) for r in range(R)]
+    epr = E // R
+    for it in range(2):
+        ins = [[x.cuda() for x in moe_inputs(r, T, H, E, topk, it, dt, zipf)] for r in range(R)]
+        toks = [i[0] for i in ins]
+        idxs = [i[1] for i in ins]
+        wts = [i[2] for i in ins]
+        totals = moe_dispatch_emulated(ctxs, toks, idxs)
+        torch.cuda.synchronize()
+        w.check()
+        seen = [set() for _ in range(R)]
+        for r in range(R):
+            n = int(totals[r].item())
+            exp_n = sum(int(((idxs[s] // epr) == r).sum()) for s in range(R))
+            assert n == exp_n
+            # segment layout: (source, local expert) in order, counts match the routing
+            counts = ctxs[r].recv_counts.cpu()
+            for s in range(R):
+                for k in range(epr):
+                    assert int(counts[s, k]) == int((idxs[s] == r * epr + k).sum())
+        for s in range(R):
+            sc = ctxs[s].scatter_idx[:T].cpu()
+            ic = idxs[s].cpu()
+            for t in range(0, T, 7):
+                for j in range(topk):
+                    d = int(ic[t, j]) // epr
+                    row = int(sc[t, j])
+                    assert torch.equal(ctxs[d].recv[row], toks[s][t])            # content
+            for t in range(T):
+                for j in range(topk):
+                    key = (int(ic[t, j]) // epr, int(sc[t, j]))
+                    assert key[1] not in seen[key[0]]                               # bijection
+                    seen[key[0]].add(key[1])
+            # rows of (s -> d, expert) fall inside their segment
+        for r in range(R):
+            n = int(totals[r].item())
+            assert seen[r] == set(range(n))
+            ctxs[r].out[:n] = fake_expert(ctxs[r].recv[:n])
+        outs = [torch.empty_like(t) for t in toks]
+        moe_combine_emulated(ctxs, idxs, outs, wts)
+        torch.cuda.synchronize()
+        w.check()
+        for s in range(R):
+            sc = ctxs[s].scatter_idx[:T].long()
+            exp = (wts[s].unsqueeze(-1) * (toks[s].float().unsqueeze(1) * 2 + (sc % 5).float().unsqueeze(-1))).sum(1)
+            assert (outs[s].float() - exp).abs().max().item() < 3e-2
+
+
+def test_bounded_wait_reports_status():
+    """A wait on a flag nothing sets runs out, records a status and leaves the context usable."""
+    from tridist_b200.parallel.runtime import TriDistError
+    w = _world1()
+    C = _loaded_native()
+    w.clear_status()
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    C.wait_flag_test(flag.data_ptr(), 7, w.status_dev, w.abort_word, 50_000_000)   # 50 ms limit
+    torch.cuda.synchronize()
+    st = w.status()
+    assert st[0] == 1 and st[2] == 32 and st[3] == 7 and st[4] == 0
+    with pytest.raises(TriDistError):
+        w.check()
+    w.clear_status()
+    w.check()
+    # the context still works
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0
+
+
+def test_spot_verify_flags_bad_tile():
+    from tridist_b200.ops._gemm_common import gemm_nt
+    C = _loaded_native()
+    torch.manual_seed(5)
+    M, N, K = 256, 512, 256
+    a = (torch.randn(M, K, device="cuda") * 0.1).to(torch.float16)
+    b = (torch.randn(N, K, device="cuda") * 0.1).to(torch.float16)
+    c = gemm_nt(a, b, bn=256)
+    bad = torch.zeros(4, dtype=torch.int32, device="cuda")
+    C.spot_verify(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, K, K, N, False, 4, 2e-2, bad.data_ptr(), 256)
+    torch.cuda.synchronize()
+    assert bad.sum().item() == 0
+    c[128:, 256:] += 1.0                                  # damage tile (1, 1)
+    C.spot_verify(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, K, K, N, False, 4, 2e-2, bad.data_ptr(), 256)
+    torch.cuda.synchronize()
+    assert bad.tolist() == [0, 0, 0, 1]

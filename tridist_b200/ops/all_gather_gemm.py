@@ -93,11 +93,8 @@ def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
     if isinstance(world, CpuWorld):
         return ctx
     assert input_dtype == output_dtype, "the fused kernel emits the input dtype"
-    ctx.ws = world.alloc(2 * max_M * K * 2)
-    ctx.flags = world.alloc(num_ranks * ctx.max_chunks * 4)
-    if isinstance(world, EmulatedWorld):
-        ctx.ws = world.view(ctx.ws, rank)
-        ctx.flags = world.view(ctx.flags, rank)
+    ctx.ws = world.alloc(2 * max_M * K * 2, rank)
+    ctx.flags = world.alloc(num_ranks * ctx.max_chunks * 4, rank)
     ctx.counters = torch.zeros(num_ranks * ctx.max_chunks, dtype=torch.int32, device="cuda")
     ctx.arrival_ns = torch.zeros(num_ranks, dtype=torch.int64, device="cuda")
     world.host_barrier()

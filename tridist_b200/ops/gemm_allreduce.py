@@ -1,0 +1,197 @@
+"""GEMM + all-reduce:  C = sum_r A_r @ B_r^T, full C on every rank (K sharded).
+
+Public API follows the reference (triton_dist/kernels/dcu/gemm_allreduce.py:250-449):
+
+* ``create_gemm_ar_intra_node_context(max_M, N, input_dtype, output_dtype, rank, num_ranks,
+  mpi, comm, M_PER_CHUNK=512, gemm_stream=None, ar_stream=None)``
+* ``gemm_ar_intra_node_op(a, b, c, ctx, component="full")`` with ``a[M, K_loc]``, ``b[N, K_loc]``,
+  ``c[M, N]``; ``component`` in {"full", "gemm", "push"} for the decomposition
+* ``gemm_ar_intra_node(a, b, ctx)`` allocates c.
+
+Two fused algorithms live in the one persistent kernel and are chosen by size:
+
+one-shot  every epilogue stores its 16-bit partial tile into all ranks' slots and
+          raises the tile ticket; every rank then sums the R partials of the tile
+          in a fixed order (bit-identical result everywhere). One NVLink hop;
+          best for small M (latency-bound decode shapes).
+two-shot  tile t is owned by rank t % R. Non-owners store their partial into the
+          owner's slot; the owner's epilogue adds them to its fp32 accumulator and
+          broadcasts the reduced tile into every rank's result buffer. 2(R-1)/R of
+          the one-shot traffic; best for large M.
+
+An NVLS (multimem) variant is not built: the symmetric heap here is CUDA-IPC
+based and has no multicast binding.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..parallel import cpu_backend
+from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
+                                native)
+from ..utils.config import env_int, env_str
+from ._gemm_common import (BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_NATURAL, SCHED_STRIDED, PlanCache,
+                           base_desc, choose_bn, rotation_order)
+
+
+@dataclass
+class GemmARContext:
+    rank: int
+    num_ranks: int
+    max_M: int
+    N: int
+    input_dtype: torch.dtype
+    output_dtype: torch.dtype
+    M_PER_CHUNK: int
+    world: object
+    slots: Optional[SymmBuffer] = None       # [2][R, max_M, N] partials by source
+    res: Optional[SymmBuffer] = None         # [2][max_M, N] reduced result (two-shot)
+    tile_flags: Optional[SymmBuffer] = None  # u32 [R, max_tiles]
+    res_flags: Optional[SymmBuffer] = None   # u32 [max_tiles]
+    flag_round: int = 0
+    plans: PlanCache = field(default_factory=PlanCache)
+    mode: str = "auto"
+
+    @property
+    def max_tiles(self) -> int:
+        return ((self.max_M + BM - 1) // BM) * ((self.N + 127) // 128)
+
+    def symm_output(self, M: int, parity: Optional[int] = None) -> torch.Tensor:
+        """The [M, N] view of the NEXT call's result buffer. Passing it as ``c`` lets the
+        two-shot kernel deliver peers' reduced tiles straight into ``c`` (no copy)."""
+        if parity is None:
+            parity = (self.flag_round + 1) & 1
+        off = parity * self.max_M * self.N * 2
+        return self.res.tensor(self.output_dtype, (M, self.N), off, rank=self.rank)
+
+
+def create_gemm_ar_intra_node_context(max_M, N, input_dtype, output_dtype, rank, num_ranks, mpi=None,
+                                      comm=None, M_PER_CHUNK=512, gemm_stream=None, ar_stream=None,
+                                      world=None):
+    """Collective. Allocates partial-slot, result and ticket planes on the symmetric heap."""
+    assert input_dtype == output_dtype, "input and output dtype must match"
+    M_PER_CHUNK = min(M_PER_CHUNK, max_M)
+    assert max_M % M_PER_CHUNK == 0 and M_PER_CHUNK % 64 == 0 and N % 128 == 0
+    assert num_ranks * max_M * N < 2 ** 31
+    if world is None:
+        world = default_world() or init_runtime(rank, num_ranks, comm)
+    ctx = GemmARContext(rank=rank, num_ranks=num_ranks, max_M=max_M, N=N, input_dtype=input_dtype,
+                        output_dtype=output_dtype, M_PER_CHUNK=M_PER_CHUNK, world=world,
+                        mode=env_str("TRIDIST_AR_MODE", "auto"))
+    if isinstance(world, CpuWorld):
+        return ctx
+    if num_ranks > 1:
+        ctx.slots = world.alloc(2 * num_ranks * max_M * N * 2, rank)
+        ctx.res = world.alloc(2 * max_M * N * 2, rank)
+        ctx.tile_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)
+        ctx.res_flags = world.alloc(ctx.max_tiles * 4, rank)
+    world.host_barrier()
+    return ctx
+
+
+def pick_mode(ctx, M: int) -> str:
+    if ctx.num_ranks == 1:
+        return "local"
+    if ctx.mode in ("one_shot", "two_shot"):
+        return ctx.mode
+    limit = env_int("TRIDIST_AR_ONE_SHOT_BYTES", 4 << 20)
+    return "one_shot" if M * ctx.N * 2 <= limit else "two_shot"
+
+
+def _plan(ctx, a, b, c, mode, parity):
+    R, rank = ctx.num_ranks, ctx.rank
+    M, K = a.shape
+    N = b.shape[0]
+    bn = choose_bn(M, N)
+    res_is_c = 0
+    if mode == "two_shot":
+        res_ptr = ctx.res.local_ptr + parity * ctx.max_M * ctx.N * 2
+        res_is_c = 1 if (c.data_ptr() == res_ptr and c.stride(0) == N) else 0
+    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0), c.stride(0),
+           a.dtype, bn, mode, res_is_c, parity if res_is_c else -1)
+
+    def make():
+        op = {"local": OP_PLAIN, "gemm": OP_PLAIN, "one_shot": OP_AR1, "two_shot": OP_AR2}[mode]
+        d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, op)
+        if op in (OP_AR1, OP_AR2):
+            half = R * ctx.max_M * ctx.N * 2
+            d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
+            d["slot_stride"] = M * N
+            d["peer_tile_flags"] = ctx.tile_flags.ptrs()
+        if op == OP_AR2:
+            d["sched"] = SCHED_STRIDED
+            d["seg_order"] = rotation_order(rank, R, 1, own_last=True)
+            rhalf = ctx.max_M * ctx.N * 2
+            d["peer_res"] = [ctx.res.ptrs(0), ctx.res.ptrs(rhalf)]
+            d["peer_res_flags"] = ctx.res_flags.ptrs()
+            d["res_is_c"] = res_is_c
+        return native().gemm_plan_create(d)
+
+    return ctx.plans.get(key, make)
+
+
+def _check_args(a, b, c, ctx):
+    M, K = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == K and a.dtype == ctx.input_dtype and b.dtype == ctx.input_dtype
+    assert M <= ctx.max_M and N == ctx.N, "shape exceeds the context"
+    assert M % 64 == 0 and K % 16 == 0
+    assert c.shape[0] == M and c.shape[1] == N and c.stride(1) == 1
+    assert a.stride(1) == 1 and b.stride(1) == 1
+
+
+def gemm_ar_intra_node_op(a, b, c, ctx, component="full"):
+    """``c[M, N] = sum over ranks of a @ b.T`` (replicated).
+
+    ``component="gemm"`` runs the local GEMM only (partial result in c, no
+    communication); ``component="push"`` is accepted for the reference's
+    decomposition benches and runs the full fused kernel, since push and GEMM
+    are one kernel here.
+    """
+    if component not in ("full", "gemm", "push"):
+        raise ValueError(f"unknown component {component!r}")
+    if isinstance(ctx.world, CpuWorld):
+        if component == "gemm":
+            c.copy_((a.float() @ b.float().t()).to(c.dtype))
+            return c
+        return cpu_backend.gemm_ar(a, b, c, ctx)
+    _check_args(a, b, c, ctx)
+    mode = "gemm" if component == "gemm" else pick_mode(ctx, a.shape[0])
+    if mode not in ("gemm", "local"):
+        ctx.flag_round += 1
+    rnd = max(ctx.flag_round, 1)
+    pid = _plan(ctx, a, b, c, mode, rnd & 1)
+    native().gemm_plan_launch(pid, rnd, rnd & 1, 0, 0)
+    return c
+
+
+def gemm_ar_intra_node(a, b, ctx):
+    """Allocating wrapper. With the two-shot algorithm the returned tensor is a view of the
+    context's symmetric result buffer (valid until the second next call on this context)."""
+    M = a.shape[0]
+    if (not isinstance(ctx.world, CpuWorld)) and pick_mode(ctx, M) == "two_shot":
+        c = ctx.symm_output(M)
+    else:
+        c = torch.empty((M, b.shape[0]), dtype=ctx.output_dtype, device=a.device)
+    return gemm_ar_intra_node_op(a, b, c, ctx)
+
+
+def gemm_ar_emulated(ctxs, a_list, b_list, c_list, mode="one_shot"):
+    for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list):
+        _check_args(a, b, c, ctx)
+        ctx.flag_round += 1
+    rnd = ctxs[0].flag_round
+    pids = [_plan(ctx, a, b, c, mode, rnd & 1) for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list)]
+    native().gemm_plans_launch_emulated(pids, rnd, rnd & 1, 0)
+    return c_list
+
+
+def finalize_gemm_ar_context(ctx) -> None:
+    ctx.plans.clear()
+    if ctx.slots is not None and not isinstance(ctx.world, EmulatedWorld):
+        for buf in (ctx.slots, ctx.res, ctx.tile_flags, ctx.res_flags):
+            ctx.world.free(buf)
+    ctx.slots = ctx.res = ctx.tile_flags = ctx.res_flags = None

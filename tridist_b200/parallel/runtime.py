@@ -132,7 +132,7 @@ class ProcessWorld(_WorldBase):
         self.barrier_buf = self.alloc(256)
 
     # -- symmetric heap ------------------------------------------------------
-    def alloc(self, nbytes: int) -> SymmBuffer:
+    def alloc(self, nbytes: int, rank: Optional[int] = None) -> SymmBuffer:
         """Collective: every rank must call with the same size, in the same order."""
         nbytes = max(256, (int(nbytes) + 255) // 256 * 256)
         local = self.C.symm_alloc(nbytes)
@@ -219,18 +219,30 @@ class EmulatedWorld(_WorldBase):
             device = torch.cuda.current_device()
         self.device = device
         self.C = native()
+        self._seq = [0] * num_ranks
+        self._shared: List[SymmBuffer] = []
         hp, dp = self.C.status_alloc()
         self.status_host, self.status_dev = hp, dp
         self.abort_buf = self.alloc(256)
         self.abort_word = self.abort_buf.peer_ptrs[0]
         self.group = None
 
-    def alloc(self, nbytes: int) -> SymmBuffer:
+    def alloc(self, nbytes: int, rank: Optional[int] = None) -> SymmBuffer:
+        """The k-th allocation of every virtual rank names the same set of R buffers,
+        as the k-th collective allocation does across processes."""
         nbytes = max(256, (int(nbytes) + 255) // 256 * 256)
-        ptrs = [self.C.symm_alloc(nbytes) for _ in range(self.num_ranks)]
-        buf = SymmBuffer(nbytes=nbytes, rank=0, peer_ptrs=ptrs, device=self.device, _owner=self)
-        self._buffers.append(buf)
-        return buf
+        if rank is None:
+            ptrs = [self.C.symm_alloc(nbytes) for _ in range(self.num_ranks)]
+            buf = SymmBuffer(nbytes=nbytes, rank=0, peer_ptrs=ptrs, device=self.device, _owner=self)
+            self._buffers.append(buf)
+            return buf
+        idx = self._seq[rank]
+        self._seq[rank] += 1
+        if idx == len(self._shared):
+            self._shared.append(self.alloc(nbytes))
+        base = self._shared[idx]
+        assert base.nbytes == nbytes, "virtual ranks must allocate the same sizes in the same order"
+        return self.view(base, rank)
 
     def view(self, buf: SymmBuffer, rank: int) -> SymmBuffer:
         return SymmBuffer(nbytes=buf.nbytes, rank=rank, peer_ptrs=buf.peer_ptrs, device=buf.device,
