@@ -474,6 +474,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // ---- routing: which rank keeps this lane's row / this tile --------------
       int owner = p.rank;
       bool tile_reduces = false;            // uniform over the CTA
+      bool tile_publishes = false;          // uniform over the CTA
       int o_lo = 0, o_hi = 0;
       if (multi) {
         if (p.op == OP_RS) {
@@ -481,41 +482,62 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           o_lo = (t.m_tile * BM) / p.m_per_rank;
           o_hi = min((min(t.m_tile * BM + BM, p.M) - 1) / p.m_per_rank, p.R - 1);
           tile_reduces = (o_lo <= p.rank && p.rank <= o_hi);
+          tile_publishes = !(o_lo == p.rank && o_hi == p.rank);
         } else if (p.op == OP_AR2) {
           owner = t.linear % p.R;
           tile_reduces = (owner == p.rank);
+          tile_publishes = !tile_reduces;
         } else if (p.op == OP_AR1) {
           tile_reduces = true;
+          tile_publishes = true;
         }
       }
 
-      if (multi && p.op == OP_AR1) {
-        // one-shot: publish the 16-bit partial into every rank's slot (own included)
+      // ---- phase 1: publish 16-bit partials into other ranks' slots --------------
+      // Always before any wait: two owners of one mixed tile would otherwise wait
+      // for each other's partial.
+      if (tile_publishes) {
         for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.n_tile * BN + c * 32;
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c * 32, r);
           tmem_ld_wait();
-          const int col = t.n_tile * BN + c * 32;
-          if (row_ok && col < p.N) {
-            float acc[32];
+          if (!row_ok || col >= p.N) continue;
+          float acc[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+          if (p.op == OP_AR1) {
             const int64_t off = static_cast<int64_t>(row) * p.N + col;
             for (int d = 0; d < p.R; ++d) {
               uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
                               (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
               store_row32<kBf16>(slot, acc);
             }
+          } else if (owner != p.rank) {
+            const int64_t off = (p.op == OP_RS)
+                ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col
+                : static_cast<int64_t>(row) * p.N + col;
+            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
+                            (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
+            store_row32<kBf16>(slot, acc);
           }
         }
         fence_acq_rel_sys();
         named_bar_sync(2, kEpiThreads);
-        if (etid < p.R && etid != p.rank)
-          st_release_sys(p.peer_tile_flags[etid] + p.rank * tiles + t.linear, p.round);
+        if (p.op == OP_RS) {
+          const int o = o_lo + etid;
+          if (o <= o_hi && o != p.rank)
+            st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + t.linear, p.round);
+        } else if (p.op == OP_AR1) {
+          if (etid < p.R && etid != p.rank)
+            st_release_sys(p.peer_tile_flags[etid] + p.rank * tiles + t.linear, p.round);
+        } else if (etid == 0) {
+          st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + t.linear, p.round);
+        }
       }
 
+      // ---- phase 2: wait for the other sources' partials of this tile -------------
       if (tile_reduces) {
-        // every other source's partial of this tile must have landed here
         bool ok = true;
         if (etid == 0) {
           for (int s = 0; ok && s < p.R; ++s) {
@@ -528,39 +550,43 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (!epi_vote(&s_flags[0], ok)) break;
       }
 
-      for (int c = 0; c < BN / 32; ++c) {
-        if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
-        float acc[32];
-        if (multi && p.op == OP_AR1) {
-          // all R contributions (own included) are summed from their 16-bit form
+      // ---- phase 3: final values of the rows / tile this rank keeps ---------------
+      const bool finalizes = !multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces;
+      if (finalizes) {
+        for (int c = 0; c < BN / 32; ++c) {
+          if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
+          float acc[32];
+          if (multi && p.op == OP_AR1) {
+            // all R contributions (own included) are summed from their 16-bit form
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-        } else if (p.epi == EPI_SWIGLU) {
-          // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
-          uint32_t g[32], u[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, g);
-          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
-          tmem_ld_wait();
+            for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+          } else if (p.epi == EPI_SWIGLU) {
+            // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
+            uint32_t g[32], u[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, g);
+            tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = silu(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-        } else {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
+            for (int j = 0; j < 32; ++j)
+              acc[j] = silu(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+          } else {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-        }
-        const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
-                                               : t.n_tile * BN + c * 32;
-        if (!row_ok || ocol >= p.N) continue;
+            for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+          }
+          const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
+                                                 : t.n_tile * BN + c * 32;
+          if (!row_ok || ocol >= p.N) continue;
 
-        if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
-          store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                 (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                             acc);
-        } else if (p.op == OP_RS) {
-          const int lrow = row - owner * p.m_per_rank;
-          if (owner == p.rank) {
+          if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
+            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                   (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                               acc);
+          } else if (p.op == OP_RS) {
+            if (owner != p.rank) continue;
+            const int lrow = row - owner * p.m_per_rank;
             // fixed source order keeps the sum deterministic
             for (int s = 0; s < p.R; ++s) {
               if (s == p.rank) continue;
@@ -572,25 +598,18 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
                                    (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
                                acc);
-          } else {
-            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
-                            (static_cast<int64_t>(p.rank) * p.slot_stride +
-                             static_cast<int64_t>(lrow) * p.N + ocol) * 2;
-            store_row32<kBf16>(slot, acc);
-          }
-        } else if (p.op == OP_AR1) {
-          const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-          for (int s = 0; s < p.R; ++s) {
-            const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
-                                  (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
-            add_row32<kBf16>(acc, slot);
-          }
-          store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                 (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                             acc);
-        } else {  // OP_AR2
-          const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-          if (owner == p.rank) {
+          } else if (p.op == OP_AR1) {
+            const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+            for (int s = 0; s < p.R; ++s) {
+              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                                    (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
+              add_row32<kBf16>(acc, slot);
+            }
+            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                   (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                               acc);
+          } else {  // OP_AR2, this rank owns the tile
+            const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
             for (int s = 0; s < p.R; ++s) {
               if (s == p.rank) continue;
               const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
@@ -605,10 +624,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
                                      (static_cast<int64_t>(row) * ldc + ocol) * 2,
                                  acc);
-          } else {
-            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
-                            (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
-            store_row32<kBf16>(slot, acc);
           }
         }
       }
@@ -618,20 +633,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
 
-      // ---- publish what this tile wrote into other ranks ----------------------
-      if (multi && (p.op == OP_RS || p.op == OP_AR2)) {
+      // ---- two-shot: tell every rank the reduced tile is in its result buffer ------
+      if (multi && p.op == OP_AR2 && tile_reduces) {
         fence_acq_rel_sys();
         named_bar_sync(2, kEpiThreads);
-        if (p.op == OP_RS) {
-          const int o = o_lo + etid;
-          if (o <= o_hi && o != p.rank)
-            st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + t.linear, p.round);
-        } else if (owner != p.rank) {
-          if (etid == 0)
-            st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + t.linear, p.round);
-        } else if (etid < p.R && etid != p.rank) {
-          st_release_sys(p.peer_res_flags[etid] + t.linear, p.round);
-        }
+        if (etid < p.R && etid != p.rank) st_release_sys(p.peer_res_flags[etid] + t.linear, p.round);
       }
       ++it;
     }
