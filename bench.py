@@ -1,0 +1,203 @@
+"""Headline benchmark: the fused communication+compute operators at the named shapes.
+
+One *step* runs every workload of BASELINE.json once (AG+GEMM and GEMM+RS at the
+GPT-3-175B MLP shape, GEMM+AR at M in {128, 1024, 4096}, the MoE all-to-all round
+with uniform and Zipf routing, and the Llama-3-70B TP-MLP layer), flushing L2
+before each operator.  Total work is fixed as the GPU count grows (strong
+scaling); at 1 GPU every operator degenerates to its local GEMM / permutation.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+      --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
+
+Rank 0 prints ONE JSON line. `value` / `ms_per_step` is the device-timed duration
+of a step (max over ranks). `ops` gives, per operator, the fused p50, the
+cuBLAS+NCCL p50 measured in the same process, and the fraction of the roofline.
+`e2e` repeats the step through the public API with the host->device copy of the
+step's activations from pinned memory and a device->host read of result digests.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "p50 ms per fused op (AG+GEMM/GEMM+RS/GEMM+AR/MoE a2a) vs cuBLAS+NCCL, 1-8 GPU"
+
+
+def reference_arm(args) -> None:
+    # The reference drives Hygon DCUs through DTK / DUSHMEM (libdushmem_host.so, libamdhip64.so,
+    # an MPI bootstrap and Triton's hcu backend); none of that exists for sm_100a.
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is DCU-only: it loads libdushmem_host.so/libamdhip64.so via ctypes and needs "
+                       "Triton's hcu backend + DTK bitcode; it has no setup.py/pyproject to install and cannot "
+                       "run on CUDA (see DESIGN.md)"}))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ops", default="", help="comma-separated subset of workloads (default: all)")
+    ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local_rank))
+
+    from bench.workloads import build_all
+    from tridist_b200.parallel.runtime import init_runtime, native
+    from tridist_b200.utils.timing import ClockSampler, flush_l2, max_over_ranks, time_op
+
+    rt = init_runtime(rank, world)
+    C = native()
+    only = [s for s in args.ops.split(",") if s] or None
+    wls = build_all(rank, world, only)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- correctness before timing (every bench of the reference does the same) --------
+    errs = {}
+    for w in wls:
+        errs[w.name] = w.check()
+        torch.cuda.synchronize()
+        rt.check()
+    sync_all()
+
+    def step(events=None):
+        for i, w in enumerate(wls):
+            flush_l2()
+            if events is not None:
+                events[i][0].record()
+            w.run()
+            if events is not None:
+                events[i][1].record()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+
+    # ---- timed region: exactly K steps -------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in wls]
+           for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = C.launch_count()
+    sync_all()
+    t0.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t1.record()
+    sync_all()
+    launches = C.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    rt.check()
+    total_ms = max_over_ranks([t0.elapsed_time(t1)])[0]
+    ms_per_step = total_ms / args.steps
+
+    ops = {}
+    for i, w in enumerate(wls):
+        per_iter = max_over_ranks([evs[k][i][0].elapsed_time(evs[k][i][1]) for k in range(args.steps)])
+        p50 = statistics.median(per_iter)
+        roof = w.roof()
+        ops[w.name] = {"fused_p50_ms": round(p50, 4), "fused_min_ms": round(min(per_iter), 4),
+                       "roofline_ms": round(roof["ms"], 4),
+                       "roofline_frac": round(roof["ms"] / p50, 3) if p50 > 0 else None,
+                       "check_max_abs_err": errs[w.name]}
+
+    # ---- cuBLAS + NCCL composition of the same operators -----------------------------------
+    if not args.no_baseline:
+        for w in wls:
+            r = time_op(w.baseline, iters=args.steps, warmup=3, flush=True)
+            ops[w.name]["cublas_nccl_p50_ms"] = round(r["p50"], 4)
+            ops[w.name]["speedup_vs_cublas_nccl"] = round(r["p50"] / ops[w.name]["fused_p50_ms"], 3)
+        sync_all()
+
+    # ---- end to end through the public API: H2D of the inputs, D2H of the result digests ----
+    e2e = None
+    if not args.no_e2e:
+        host_out = torch.empty(len(wls), dtype=torch.float32).pin_memory()
+        dev_out = torch.empty(len(wls), dtype=torch.float32, device="cuda")
+
+        def e2e_step():
+            for i, w in enumerate(wls):
+                flush_l2()
+                w.stage()
+                w.run()
+                dev_out[i] = w.digest()
+            host_out.copy_(dev_out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        sync_all()
+        e2e_ms = max_over_ranks([e0.elapsed_time(e1)])[0] / args.steps
+        e2e = {"value": round(e2e_ms, 4), "unit": "ms/step",
+               "h2d_bytes_per_step": int(sum(w.h2d_bytes for w in wls)),
+               "d2h_bytes_per_step": int(host_out.numel() * 4)}
+        rt.check()
+
+    if rank == 0:
+        names = [w.name for w in wls]
+        out = {
+            "metric": METRIC, "value": round(ms_per_step, 4), "unit": "ms/step", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp16+bf16",
+            "data": "synthetic seeded inputs, random-init weights of the named shapes",
+            "impl": "ours",
+            "config": {
+                "model": "GPT-3-175B MLP (AG+GEMM, GEMM+RS) + GEMM+AR K=28672 N=8192 M in {128,1024,4096} + "
+                         "MoE a2a E64 H4096 T4096/rank topk8 (uniform, Zipf 1.2) + Llama-3-70B TP-MLP fwd",
+                "global_batch": 8192, "seq_len": 1, "parallelism": f"tp{world}" + ("+ep%d" % world),
+                "step": "one run of each workload: " + ",".join(names),
+                "l2": "256 MB buffer overwritten before every operator (inside the step time)",
+                "timing": "CUDA events on the launching stream, max over ranks",
+            },
+            "ops": ops, "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e is not None:
+            out["e2e"] = e2e
+        print(json.dumps(out))
+    sync_all()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
