@@ -29,6 +29,7 @@ SOURCES = [
     "ops/fused_gemm.cu",
     "ops/elementwise.cu",
     "ops/moe_a2a.cu",
+    "ops/moe_local_noalloc.cu",
 ]
 
 NVCC_FLAGS = [
