@@ -58,24 +58,39 @@ class GemmARBaseline:
 
 
 class MoEBaseline:
-    """Equal-split padded all_to_all_single for dispatch and for combine; the padded
-    capacity per (source, destination) pair is every pair of the source (worst case),
-    as in the reference's bench (bench/s9_bench_8card.py:332-340 uses equal splits)."""
+    """all_to_all_single for dispatch and again for combine, carrying exactly the rows the
+    routing sends between each pair of ranks (uneven splits). The reference's bench uses equal
+    padded splits (bench/s9_bench_8card.py:332-340); exact splits move fewer bytes and are the
+    stronger baseline, and they stay meaningful under skewed routing."""
 
-    def __init__(self, T, H, topk, R, dtype, group=None, cap_rows=None):
+    def __init__(self, idx, E, H, R, dtype, group=None):
         self.R, self.group = R, group
-        # with uniform routing a destination receives about T*topk/R rows from each source;
-        # use that (rounded up by 25 %) as the fixed per-pair capacity
-        cap = cap_rows or (int(T * topk / R * 1.25) + 8)
-        self.cap = cap
-        self.send = torch.empty((R * cap, H), dtype=dtype, device="cuda")
-        self.recv = torch.empty((R * cap, H), dtype=dtype, device="cuda")
-        self.back = torch.empty((R * cap, H), dtype=dtype, device="cuda")
+        epr = E // R
+        dest = (idx.long() // epr).flatten()
+        send = torch.bincount(dest, minlength=R).to(torch.int64)            # rows I send to each rank
+        if R > 1:
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=group)
+        else:
+            recv = send.clone()
+        self.send_splits = send.cpu().tolist()
+        self.recv_splits = recv.cpu().tolist()
+        rank = dist.get_rank(group) if R > 1 else 0
+        mine_in = sum(v for i, v in enumerate(self.recv_splits) if i != rank)
+        mine_out = sum(v for i, v in enumerate(self.send_splits) if i != rank)
+        if R > 1:
+            t = torch.tensor([mine_in, mine_out], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+            mine_in, mine_out = int(t[0]), int(t[1])
+        self.recv_splits_remote_rows, self.send_splits_remote_rows = mine_in, mine_out
+        self.send = torch.empty((sum(self.send_splits), H), dtype=dtype, device="cuda")
+        self.recv = torch.empty((sum(self.recv_splits), H), dtype=dtype, device="cuda")
+        self.back = torch.empty_like(self.send)
 
     def __call__(self):
         if self.R > 1:
-            dist.all_to_all_single(self.recv, self.send, group=self.group)
-            dist.all_to_all_single(self.back, self.recv, group=self.group)
+            dist.all_to_all_single(self.recv, self.send, self.recv_splits, self.send_splits, group=self.group)
+            dist.all_to_all_single(self.back, self.recv, self.send_splits, self.recv_splits, group=self.group)
         else:
             self.recv.copy_(self.send)
             self.back.copy_(self.recv)

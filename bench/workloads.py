@@ -172,7 +172,7 @@ class MoE(Workload):
         self.tokens, self.idx, self.wts = self.tok_host.cuda(), self.idx_host.cuda(), self.w_host.cuda()
         self.out = torch.empty_like(self.tokens)
         self.ctx = create_moe_a2a_intra_node_context(E, H, dtype, T, topk, rank, R)
-        self.base = baselines.MoEBaseline(T, H, topk, R, dtype)
+        self.base = baselines.MoEBaseline(self.idx, E, H, R, dtype)
         self.h2d_bytes = tokens.numel() * 2 + idx.numel() * 4 + wts.numel() * 4
         self.n_rows = None
 
@@ -196,7 +196,12 @@ class MoE(Workload):
         return self.out[0, :8].float().sum()
 
     def roof(self):
-        return roofline.moe_roof(self.T, self.H, self.topk, self.R)
+        # the busiest rank bounds the round: rows it receives (dispatch) and serves (combine)
+        r = roofline.moe_roof(self.T, self.H, self.topk, self.R)
+        if self.R > 1:
+            hot = max(self.base.recv_splits_remote_rows, self.base.send_splits_remote_rows)
+            r = roofline.roof_ms(0.0, 2.0 * hot * self.H * 2)
+        return r
 
     def check(self):
         self.run()

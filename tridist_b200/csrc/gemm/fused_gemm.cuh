@@ -54,6 +54,14 @@ enum SchedMode : int32_t {
   SCHED_LIST = 3,      // explicit list of row-major tile ids (repair of flagged tiles)
 };
 
+// Epilogue staging: each accumulator row gets 256 data bytes (128 columns) at a pitch of
+// 272 bytes, so that the 16-byte stores of 8 consecutive rows hit different banks while
+// every row stays contiguous for the bulk copy that ships it.
+constexpr int kStageCols = 128;
+constexpr int kStageRowBytes = kStageCols * 2;
+constexpr int kStagePitch = kStageRowBytes + 16;
+constexpr int kStagingBytes = BM * kStagePitch;
+
 template <int BN>
 struct TileShape {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -61,8 +69,9 @@ struct TileShape {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;
-  // ring + 1 KB for barriers and the TMEM slot + 1 KB alignment slack
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+  // ring + epilogue staging (one padded 256-byte row per accumulator row) + 1 KB for
+  // barriers and the TMEM slot; the dynamic shared array is declared 1024-byte aligned
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
 };
 
 struct alignas(64) GemmParams {
@@ -263,11 +272,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // indexes the rank and each rank reads its own parameter block.
   const GemmParams& p = pv ? pv[blockIdx.y] : p0;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TS::kStages * TS::kStageBytes);
+  uint8_t* staging = smem + TS::kStages * TS::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + TS::kStages;
   uint64_t* tmem_full_bar = bars + 2 * TS::kStages;
@@ -346,8 +354,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                 ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck);
                 if (ok) {
                   if (ck < 32) ready_mask[src] |= 1u << ck;
-                  if (p.arrival_ns != nullptr && ck == 0 && blockIdx.x == 0)
-                    p.arrival_ns[src] = globaltimer_ns();
+                  if (p.arrival_ns != nullptr && ck == 0)
+                    atomicMin(reinterpret_cast<unsigned long long*>(p.arrival_ns + src),
+                              static_cast<unsigned long long>(globaltimer_ns()));
                 }
               }
               if (!ok) break;
@@ -497,31 +506,49 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // Always before any wait: two owners of one mixed tile would otherwise wait
       // for each other's partial.
       if (tile_publishes) {
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = t.n_tile * BN + c * 32;
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (!row_ok || col >= p.N) continue;
-          float acc[32];
+        // Each thread owns one accumulator row: it converts 128 columns into its staging
+        // row, then ships the 256 contiguous bytes to every destination with one bulk
+        // copy each (large NVLink writes instead of scattered 16-byte stores).
+        uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
+        for (int half = 0; half < BN / kStageCols; ++half) {
+          const int col0 = t.n_tile * BN + half * kStageCols;
+          tma_store_wait_read<0>();          // my previous copies have read this row
+#pragma unroll 1
+          for (int c = 0; c < kStageCols / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + half * kStageCols + c * 32, r);
+            tmem_ld_wait();
+            uint4* d4 = reinterpret_cast<uint4*>(my_stage + c * 64);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
-          if (p.op == OP_AR1) {
-            const int64_t off = static_cast<int64_t>(row) * p.N + col;
-            for (int d = 0; d < p.R; ++d) {
-              uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
-                              (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
-              store_row32<kBf16>(slot, acc);
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              d4[v] = o;
             }
-          } else if (owner != p.rank) {
-            const int64_t off = (p.op == OP_RS)
-                ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col
-                : static_cast<int64_t>(row) * p.N + col;
-            uint8_t* slot = reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
-                            (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2;
-            store_row32<kBf16>(slot, acc);
           }
+          fence_proxy_async_smem();          // generic smem writes -> visible to the bulk copy
+          if (row_ok && col0 < p.N) {
+            if (p.op == OP_AR1) {
+              const int64_t off = static_cast<int64_t>(row) * p.N + col0;
+              for (int d = 0; d < p.R; ++d)
+                bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
+                                  (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
+                              my_stage, kStageRowBytes);
+            } else if (owner != p.rank) {
+              const int64_t off = (p.op == OP_RS)
+                  ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col0
+                  : static_cast<int64_t>(row) * p.N + col0;
+              bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
+                                (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
+                            my_stage, kStageRowBytes);
+            }
+          }
+          tma_store_commit();
         }
+        tma_store_wait_all<0>();             // every byte has been written
         fence_acq_rel_sys();
         named_bar_sync(2, kEpiThreads);
         if (p.op == OP_RS) {
@@ -553,8 +580,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // ---- phase 3: final values of the rows / tile this rank keeps ---------------
       const bool finalizes = !multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces;
       if (finalizes) {
+        const bool bcast = multi && p.op == OP_AR2;   // reduced tile goes out through staging
+        uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
         for (int c = 0; c < BN / 32; ++c) {
           if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
+          if (bcast && (c & 3) == 0) tma_store_wait_read<0>();
           float acc[32];
           if (multi && p.op == OP_AR1) {
             // all R contributions (own included) are summed from their 16-bit form
@@ -616,16 +646,34 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                                     (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
               add_row32<kBf16>(acc, slot);
             }
-            for (int d = 0; d < p.R; ++d) {
-              if (d == p.rank && !p.res_is_c) continue;
-              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.peer_res[d]) + off * 2, acc);
+            uint4* d4 = reinterpret_cast<uint4*>(my_stage + (c & 3) * 64);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack2<kBf16>(acc[v * 8 + 0], acc[v * 8 + 1]);
+              o.y = pack2<kBf16>(acc[v * 8 + 2], acc[v * 8 + 3]);
+              o.z = pack2<kBf16>(acc[v * 8 + 4], acc[v * 8 + 5]);
+              o.w = pack2<kBf16>(acc[v * 8 + 6], acc[v * 8 + 7]);
+              d4[v] = o;
             }
-            if (!p.res_is_c)
-              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                     (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                                 acc);
+            if ((c & 3) == 3) {
+              // 128 reduced columns of this row are staged: one bulk copy per destination
+              fence_proxy_async_smem();
+              const int64_t off0 = static_cast<int64_t>(row) * p.N + (ocol - 96);
+              for (int d = 0; d < p.R; ++d) {
+                if (d == p.rank && !p.res_is_c) continue;
+                bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_res[d]) + off0 * 2, my_stage,
+                              kStageRowBytes);
+              }
+              if (!p.res_is_c)
+                bulk_store_1d(reinterpret_cast<uint8_t*>(p.c) +
+                                  (static_cast<int64_t>(row) * ldc + (ocol - 96)) * 2,
+                              my_stage, kStageRowBytes);
+              tma_store_commit();
+            }
           }
         }
+        if (bcast) tma_store_wait_all<0>();
       }
 
       // accumulator drained: hand the TMEM buffer back to the MMA warp

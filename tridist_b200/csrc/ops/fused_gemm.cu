@@ -104,6 +104,10 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
   if (d.bn != 128 && d.bn != 256) throw std::runtime_error("tridist_b200: BN must be 128 or 256");
   if (d.epi == EPI_SWIGLU && d.bn != 256)
     throw std::runtime_error("tridist_b200: the SwiGLU epilogue needs BN = 256");
+  if (d.R > 1 && (d.op == OP_RS || d.op == OP_AR1 || d.op == OP_AR2) && d.N % 128 != 0)
+    throw std::runtime_error("tridist_b200: GEMM+RS / GEMM+AR need N % 128 == 0");
+  if (d.op == OP_AR2 && d.R > 1 && d.ldc % 8 != 0)
+    throw std::runtime_error("tridist_b200: GEMM+AR needs a 16-byte aligned row stride of c");
   if (d.K % 8 != 0) throw std::runtime_error("tridist_b200: K must be a multiple of 8");
   if (d.N % 8 != 0) throw std::runtime_error("tridist_b200: N must be a multiple of 8");
   auto* plan = new GemmPlan();
