@@ -63,6 +63,7 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   g.list_len = get<int>(d, "list_len", 0);
   g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);
   g.max_ctas = get<int>(d, "max_ctas", 0);
+  g.allow_pair = get<int>(d, "allow_pair", 1);
   fill_ptrs2(d, "peer_ws", g.peer_ws);
   fill_ptrs(d, "peer_ag_flags", g.peer_ag_flags, 8);
   g.ag_counters = get<int64_t>(d, "ag_counters", 0);

@@ -62,12 +62,14 @@ constexpr int kStageRowBytes = kStageCols * 2;
 constexpr int kStagePitch = kStageRowBytes + 16;
 constexpr int kStagingBytes = BM * kStagePitch;
 
-template <int BN>
+template <int BN, int kCtaM>
 struct TileShape {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  // kCtaM = 2: two CTAs (one cluster) share each tcgen05 MMA; a pair owns a 256 x BN
+  // output tile, every CTA loads its own 128 rows of A and its own BN/2 rows of B.
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = (BN / kCtaM) * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;
   // ring + epilogue staging (one padded 256-byte row per accumulator row) + 1 KB for
   // barriers and the TMEM slot; the dynamic shared array is declared 1024-byte aligned
@@ -83,7 +85,9 @@ struct alignas(64) GemmParams {
   int32_t m_tiles, n_tiles, k_blocks;
   int32_t rank, R;
   int32_t op, epi, sched;
-  int32_t seg_m_tiles;     // m-tiles per segment (SCHED_SEGMENT)
+  int32_t cta_m;           // CTAs per scheduling unit along M (1, or 2 for CTA pairs)
+  int32_t unit_m;          // scheduling units along M = ceil(m_tiles / cta_m)
+  int32_t seg_m_tiles;     // units per segment (SCHED_SEGMENT)
   int32_t seg_order[kMaxRanks];
   const int32_t* order_table;  // optional device table overriding seg_order (R entries)
   const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
@@ -121,7 +125,7 @@ struct alignas(64) GemmParams {
 // Tile order
 // ----------------------------------------------------------------------------
 struct TileCoord {
-  int m_tile, n_tile, linear;
+  int m_tile, n_tile, linear, owner_key;
   bool valid;
 };
 
@@ -138,46 +142,47 @@ __device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, 
   nt = r / gm;
 }
 
-__device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos) {
+// The schedule enumerates *units*: one unit is one BN-wide column block of cta_m
+// consecutive m-tiles (cta_m = 2 for CTA pairs; CTA `sub` of the pair owns m-tile
+// unit_m * cta_m + sub). `linear` indexes the tile's ticket words; `owner_key` is the
+// unit id that decides the owning rank in the strided (two-shot all-reduce) order.
+__device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos,
+                                             int sub) {
   TileCoord t;
   t.valid = true;
+  int um = 0, nt = 0, ulin = -1;
   if (p.sched == SCHED_SEGMENT) {
     const int per_seg = p.seg_m_tiles * p.n_tiles;
     const int si = pos / per_seg;
     const int u = pos - si * per_seg;
-    int mt, nt;
-    raster_grouped(u, p.seg_m_tiles, p.n_tiles, mt, nt);
-    t.m_tile = order[si] * p.seg_m_tiles + mt;
-    t.n_tile = nt;
+    raster_grouped(u, p.seg_m_tiles, p.n_tiles, um, nt);
+    um += order[si] * p.seg_m_tiles;
   } else if (p.sched == SCHED_STRIDED) {
-    const int total = p.m_tiles * p.n_tiles;
+    const int total = p.unit_m * p.n_tiles;
     const int per_owner = (total + p.R - 1) / p.R;
     const int oi = pos / per_owner;
     const int k = pos - oi * per_owner;
-    const int lin = order[oi] + k * p.R;
-    if (lin >= total) {
-      t.valid = false;
-      t.m_tile = t.n_tile = 0;
-    } else {
-      raster_grouped(lin, p.m_tiles, p.n_tiles, t.m_tile, t.n_tile);
-    }
-    // ownership and tickets are keyed by the pre-raster id (owner = id % R)
-    t.linear = lin;
-    return t;
+    ulin = order[oi] + k * p.R;
+    if (ulin >= total) t.valid = false;
+    else raster_grouped(ulin, p.unit_m, p.n_tiles, um, nt);
   } else if (p.sched == SCHED_LIST) {
     const int lin = p.tile_list[pos];
-    t.valid = lin >= 0 && lin < p.m_tiles * p.n_tiles;
-    t.m_tile = t.valid ? lin / p.n_tiles : 0;
-    t.n_tile = t.valid ? lin - t.m_tile * p.n_tiles : 0;
+    t.valid = lin >= 0 && lin < p.unit_m * p.n_tiles;
+    um = t.valid ? lin / p.n_tiles : 0;
+    nt = t.valid ? lin - um * p.n_tiles : 0;
   } else {
-    raster_grouped(pos, p.m_tiles, p.n_tiles, t.m_tile, t.n_tile);
+    raster_grouped(pos, p.unit_m, p.n_tiles, um, nt);
   }
-  t.linear = t.m_tile * p.n_tiles + t.n_tile;
+  t.m_tile = um * p.cta_m + sub;
+  t.n_tile = nt;
+  t.owner_key = ulin;
+  // ownership is keyed by the pre-raster unit id; every tile still has its own ticket
+  t.linear = (p.sched == SCHED_STRIDED) ? ulin * p.cta_m + sub : t.m_tile * p.n_tiles + nt;
   return t;
 }
 
 __device__ __forceinline__ int sched_positions(const GemmParams& p) {
-  const int total = p.m_tiles * p.n_tiles;
+  const int total = p.unit_m * p.n_tiles;
   if (p.sched == SCHED_STRIDED) return ((total + p.R - 1) / p.R) * p.R;
   if (p.sched == SCHED_LIST) return p.list_len;
   return total;
@@ -264,10 +269,11 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 // ----------------------------------------------------------------------------
 // The kernel
 // ----------------------------------------------------------------------------
-template <int BN, bool kBf16>
+template <int BN, bool kBf16, int kCtaM>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __restrict__ pv) {
-  using TS = TileShape<BN>;
+  using TS = TileShape<BN, kCtaM>;
+  static_assert(kCtaM == 1 || BN == 256, "CTA pairs are built for 256-wide tiles only");
   // With pv != nullptr the launch emulates several ranks on one GPU: grid.y
   // indexes the rank and each rank reads its own parameter block.
   const GemmParams& p = pv ? pv[blockIdx.y] : p0;
@@ -288,6 +294,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // CTA pair: rank 0 of the cluster is the leader (issues the MMAs, owns the full and
+  // TMEM-empty barriers the pair synchronises on).
+  const int sub = (kCtaM == 2) ? static_cast<int>(cluster_ctarank()) : 0;
+  const bool leader = sub == 0;
+  const int unit0 = static_cast<int>(blockIdx.x) / kCtaM;
+  const int unit_stride = static_cast<int>(gridDim.x) / kCtaM;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TS::kStages; ++s) {
@@ -296,7 +308,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 4);
+      mbar_init(&tmem_empty_bar[b], 4 * kCtaM);
     }
     mbar_init(drain_bar, 1);
     s_flags[0] = 0;
@@ -308,11 +320,17 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     s_order[i] = (p.order_table != nullptr && i < p.R) ? p.order_table[i] : p.seg_order[i];
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TS::kTmemCols);
-    tmem_relinquish();
+    if constexpr (kCtaM == 2) {
+      tmem_alloc_pair(tmem_slot, TS::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TS::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kCtaM == 2) cluster_sync_all();   // the peer's barriers are initialised too
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
@@ -331,8 +349,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       uint32_t ready_mask[kMaxRanks] = {0};   // chunks of each source already observed
       uint32_t pending = 0;                   // stages with a load in flight (bitmask)
       bool ok = true;
-      for (int pos = blockIdx.x; ok && pos < positions; pos += gridDim.x) {
-        const TileCoord t = tile_at(p, s_order, pos);
+      for (int pos = unit0; ok && pos < positions; pos += unit_stride) {
+        const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
         const int m0 = t.m_tile * BM;
         const int n0 = t.n_tile * BN;
@@ -372,18 +390,28 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           pending &= ~(1u << stage);
           uint8_t* sa = ring + stage * TS::kStageBytes;
           uint8_t* sb = sa + TS::kABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], TS::kStageBytes);
-          tma_load_2d(sa, amap, &full_bar[stage], kb * BK, a_row);
-          if (p.epi == EPI_SWIGLU) {
-            // gate rows and the matching up rows form one BN-wide virtual tile
-            tma_load_2d(sb, &p.tma_b, &full_bar[stage], kb * BK, t.n_tile * (BN / 2));
-            tma_load_2d(sb + (BN / 2) * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
-                        p.swiglu_up_row0 + t.n_tile * (BN / 2));
+          if constexpr (kCtaM == 2) {
+            // the leader's barrier collects the bytes of both CTAs' loads
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * TS::kStageBytes);
+            tma_load_2d_pair(sa, amap, &full_bar[stage], kb * BK, a_row);
+            const int b_row = (p.epi == EPI_SWIGLU)
+                ? (sub == 0 ? t.n_tile * (BN / 2) : p.swiglu_up_row0 + t.n_tile * (BN / 2))
+                : n0 + sub * (BN / 2);
+            tma_load_2d_pair(sb, &p.tma_b, &full_bar[stage], kb * BK, b_row);
           } else {
+            mbar_arrive_expect_tx(&full_bar[stage], TS::kStageBytes);
+            tma_load_2d(sa, amap, &full_bar[stage], kb * BK, a_row);
+            if (p.epi == EPI_SWIGLU) {
+              // gate rows and the matching up rows form one BN-wide virtual tile
+              tma_load_2d(sb, &p.tma_b, &full_bar[stage], kb * BK, t.n_tile * (BN / 2));
+              tma_load_2d(sb + (BN / 2) * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
+                          p.swiglu_up_row0 + t.n_tile * (BN / 2));
+            } else {
 #pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tma_load_2d(sb + h * 128 * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
-                          n0 + h * 128);
+              for (int h = 0; h < BN / 128; ++h)
+                tma_load_2d(sb + h * 128 * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
+                            n0 + h * 128);
+            }
           }
           pending |= 1u << stage;
           if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
@@ -399,7 +427,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           WaitEnv quiet = env;
           quiet.status = nullptr;
           quiet.abort_word = nullptr;
-          wait_mbar(&full_bar[s], par, quiet, SITE_PIPE_FULL, s);
+          quiet.timeout_ns = 2000000ull;   // loads land within microseconds; never linger here
+          if (leader) wait_mbar(&full_bar[s], par, quiet, SITE_PIPE_FULL, s);
         }
       }
     }
@@ -408,13 +437,13 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // warp 1: MMA issuer
   // ==========================================================================
   else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(kBf16, BM, BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBf16, BM * kCtaM, BN);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
-      for (int pos = blockIdx.x; ok && pos < positions; pos += gridDim.x) {
-        const TileCoord t = tile_at(p, s_order, pos);
+      for (int pos = unit0; ok && pos < positions; pos += unit_stride) {
+        const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
@@ -433,19 +462,28 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // +32 bytes per K step inside the 128-byte swizzle row
-            umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2),
-                        idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (kCtaM == 2)
+              umma_f16_ss_pair(d_tmem, da + static_cast<uint64_t>(k * 2),
+                               db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * 2),
+                          db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);   // frees the smem stage when these MMAs retire
+          // frees the smem stage (in both CTAs of a pair) when these MMAs retire
+          if constexpr (kCtaM == 2) umma_commit_pair_both(&empty_bar[stage]);
+          else umma_commit(&empty_bar[stage]);
           if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(&tmem_full_bar[buf]);   // accumulator complete
+        // accumulator complete (each CTA of a pair reads its own 128 rows)
+        if constexpr (kCtaM == 2) umma_commit_pair_both(&tmem_full_bar[buf]);
+        else umma_commit(&tmem_full_bar[buf]);
         ++it;
       }
       if (!ok) {
         // Unwinding: MMAs already issued must retire before TMEM is freed.
-        umma_commit(drain_bar);
+        if constexpr (kCtaM == 2) umma_commit_pair_local(drain_bar);
+        else umma_commit(drain_bar);
         WaitEnv quiet = env;
         quiet.status = nullptr;
         quiet.abort_word = nullptr;
@@ -460,11 +498,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int etid = (warp - kEpiWarp0) * 32 + lane;
     const int64_t ldc = p.ldc;
-    const int tiles = p.m_tiles * p.n_tiles;
+    const int tiles = p.unit_m * p.cta_m * p.n_tiles;   // ticket words per source
     const bool multi = p.R > 1;
     int it = 0;
-    for (int pos = blockIdx.x; pos < positions; pos += gridDim.x) {
-      const TileCoord t = tile_at(p, s_order, pos);
+    for (int pos = unit0; pos < positions; pos += unit_stride) {
+      const TileCoord t = tile_at(p, s_order, pos, sub);
       if (!t.valid) continue;
       const int buf = it & 1;
       const uint32_t use = static_cast<uint32_t>(it >> 1);
@@ -485,7 +523,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       bool tile_reduces = false;            // uniform over the CTA
       bool tile_publishes = false;          // uniform over the CTA
       int o_lo = 0, o_hi = 0;
-      if (multi) {
+      // a pair's second CTA can fall past the last row block when m_tiles is odd
+      const bool tile_has_rows = t.m_tile * BM < p.M;
+      if (multi && tile_has_rows) {
         if (p.op == OP_RS) {
           owner = min(row / p.m_per_rank, p.R - 1);
           o_lo = (t.m_tile * BM) / p.m_per_rank;
@@ -493,7 +533,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           tile_reduces = (o_lo <= p.rank && p.rank <= o_hi);
           tile_publishes = !(o_lo == p.rank && o_hi == p.rank);
         } else if (p.op == OP_AR2) {
-          owner = t.linear % p.R;
+          owner = t.owner_key % p.R;
           tile_reduces = (owner == p.rank);
           tile_publishes = !tile_reduces;
         } else if (p.op == OP_AR1) {
@@ -578,7 +618,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       }
 
       // ---- phase 3: final values of the rows / tile this rank keeps ---------------
-      const bool finalizes = !multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces;
+      const bool finalizes =
+          tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
         const bool bcast = multi && p.op == OP_AR2;   // reduced tile goes out through staging
         uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
@@ -679,7 +720,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // accumulator drained: hand the TMEM buffer back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+      if (lane == 0) {
+        if constexpr (kCtaM == 2) mbar_arrive_leader(&tmem_empty_bar[buf]);
+        else mbar_arrive(&tmem_empty_bar[buf]);
+      }
 
       // ---- two-shot: tell every rank the reduced tile is in its result buffer ------
       if (multi && p.op == OP_AR2 && tile_reduces) {
@@ -739,10 +783,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     } else if (p.op == OP_AR2 && p.R > 1) {
       // Collect the reduced tiles other owners broadcast into this rank's result
       // buffer; copy them into the caller's tensor unless it aliases the buffer.
-      const int tiles = p.m_tiles * p.n_tiles;
+      const int tickets = p.unit_m * p.cta_m * p.n_tiles;
       bool ok = true;
-      for (int lin = blockIdx.x; ok && lin < tiles; lin += gridDim.x) {
-        if (lin % p.R == p.rank) continue;
+      for (int lin = blockIdx.x; ok && lin < tickets; lin += gridDim.x) {
+        const int unit = lin / p.cta_m;
+        if (unit % p.R == p.rank) continue;
+        int um, nt;
+        raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
+        const int mt = um * p.cta_m + (lin - unit * p.cta_m);
+        if (mt * BM >= p.M) continue;         // nothing is ever published for an empty row block
         if (ctid == 0)
           ok = wait_flag_ge(p.peer_res_flags[p.rank] + lin, p.round, env, SITE_AR_RESULT, lin);
         // all comm threads learn the outcome; also orders their loads after the acquire
@@ -751,9 +800,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         ok = s_flags[1] != 0;
         named_bar_sync(1, kCommThreads);
         if (!ok || p.res_is_c) continue;
-        int mt, nt;
-        raster_grouped(lin, p.m_tiles, p.n_tiles, mt, nt);
-        // raster_grouped is the inverse map used by tile_at for natural/strided order
         const int rows = min(BM, p.M - mt * BM);
         const int cols = min(BN, p.N - nt * BN);
         const int v_per_row = cols >> 3;
@@ -774,11 +820,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // ==========================================================================
   // teardown
   // ==========================================================================
+  // A pair leaves together: neither CTA may exit while the other can still signal its
+  // barriers or issue MMAs that write its tensor memory.
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kCtaM == 2) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TS::kTmemCols);
+    if constexpr (kCtaM == 2) tmem_dealloc_pair(tmem_base, TS::kTmemCols);
+    else tmem_dealloc(tmem_base, TS::kTmemCols);
   }
 }
 

@@ -65,6 +65,7 @@ struct GemmPlan {
   GemmParams prm[2];
   int bn;
   bool bf16;
+  int cta_m;
   int grid_x;
   GemmParams* dev_params = nullptr;   // emulated multi-rank launches only
 };
@@ -87,13 +88,13 @@ static int num_sms() {
   return n;
 }
 
-template <int BN, bool kBf16>
+template <int BN, bool kBf16, int kCtaM>
 static void set_attr_once() {
   static bool done = false;
   if (!done) {
-    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16>,
+    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16, kCtaM>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               TileShape<BN>::kSmemBytes),
+                               TileShape<BN, kCtaM>::kSmemBytes),
           "cudaFuncSetAttribute(smem)");
     done = true;
   }
@@ -113,6 +114,13 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
   auto* plan = new GemmPlan();
   plan->bn = d.bn;
   plan->bf16 = d.bf16;
+  // CTA pairs (one 2-CTA tcgen05 MMA per 256 x 256 output tile) where the schedule allows
+  {
+    const int mt = (d.M + BM - 1) / BM;
+    bool pair = d.allow_pair && d.bn == 256 && mt >= 2 && d.sched != SCHED_LIST;
+    if (d.sched == SCHED_SEGMENT && ((mt / d.R) % 2 != 0)) pair = false;
+    plan->cta_m = pair ? 2 : 1;
+  }
   const int bn_out = (d.epi == EPI_SWIGLU) ? d.bn / 2 : d.bn;
   for (int par = 0; par < 2; ++par) {
     GemmParams& p = plan->prm[par];
@@ -124,7 +132,9 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.rank = d.rank; p.R = d.R;
     p.op = d.op; p.epi = d.epi; p.sched = d.sched;
     p.m_per_rank = d.m_per_rank > 0 ? d.m_per_rank : d.M;
-    p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? p.m_tiles / d.R : p.m_tiles;
+    p.cta_m = plan->cta_m;
+    p.unit_m = (p.m_tiles + p.cta_m - 1) / p.cta_m;
+    p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? (p.m_tiles / d.R) / p.cta_m : p.unit_m;
     if (d.sched == SCHED_SEGMENT && (p.m_tiles % d.R != 0 || p.m_per_rank % BM != 0))
       throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
     for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
@@ -167,13 +177,15 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
   }
   {
     const GemmParams& p = plan->prm[0];
-    int positions = p.m_tiles * p.n_tiles;
+    int positions = p.unit_m * p.n_tiles;
     if (p.sched == SCHED_STRIDED) positions = ((positions + p.R - 1) / p.R) * p.R;
     if (p.sched == SCHED_LIST) positions = p.list_len;
     int g = d.max_ctas > 0 ? d.max_ctas : num_sms();
     if (g > num_sms()) g = num_sms();
-    plan->grid_x = positions < g ? positions : g;
-    if (plan->grid_x < 1) plan->grid_x = 1;
+    g /= plan->cta_m;                       // units that can run at once
+    int units = positions < g ? positions : g;
+    if (units < 1) units = 1;
+    plan->grid_x = units * plan->cta_m;
   }
   std::lock_guard<std::mutex> lk(g_mu);
   const int64_t id = g_next_plan++;
@@ -197,12 +209,24 @@ static GemmPlan* find_plan(int64_t id) {
   return it->second;
 }
 
-template <int BN, bool kBf16>
+template <int BN, bool kBf16, int kCtaM>
 static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
-  set_attr_once<BN, kBf16>();
-  fused_gemm_kernel<BN, kBf16>
-      <<<dim3(grid_x, 1, 1), dim3(kThreads, 1, 1), TileShape<BN>::kSmemBytes, stream>>>(p, nullptr);
-  check(cudaGetLastError(), "fused_gemm_kernel launch");
+  set_attr_once<BN, kBf16, kCtaM>();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid_x, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = TileShape<BN, kCtaM>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtaM;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const GemmParams* none = nullptr;
+  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM>, p, none),
+        "fused_gemm_kernel launch");
 }
 
 void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm,
@@ -214,26 +238,31 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
   p.order_table = reinterpret_cast<const int32_t*>(order_table);
   p.skip_comm = skip_comm;
   if (plan->bn == 256) {
-    if (plan->bf16) launch_one<256, true>(p, plan->grid_x, stream);
-    else launch_one<256, false>(p, plan->grid_x, stream);
+    if (plan->cta_m == 2) {
+      if (plan->bf16) launch_one<256, true, 2>(p, plan->grid_x, stream);
+      else launch_one<256, false, 2>(p, plan->grid_x, stream);
+    } else {
+      if (plan->bf16) launch_one<256, true, 1>(p, plan->grid_x, stream);
+      else launch_one<256, false, 1>(p, plan->grid_x, stream);
+    }
   } else {
-    if (plan->bf16) launch_one<128, true>(p, plan->grid_x, stream);
-    else launch_one<128, false>(p, plan->grid_x, stream);
+    if (plan->bf16) launch_one<128, true, 1>(p, plan->grid_x, stream);
+    else launch_one<128, false, 1>(p, plan->grid_x, stream);
   }
   ++g_launches;
 }
 
 template <int BN, bool kBf16>
 static void launch_emulated(const GemmParams* dev, int grid_x, int vranks, cudaStream_t stream) {
-  set_attr_once<BN, kBf16>();
+  set_attr_once<BN, kBf16, 1>();
   GemmParams dummy;
   std::memset(&dummy, 0, sizeof(dummy));
   void* args[2] = {&dummy, &dev};
   // Cooperative launch: the runtime refuses the launch unless every CTA of
   // every emulated rank can be resident at once, which the cross-rank waits need.
-  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16>),
+  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1>),
                                     dim3(grid_x, vranks, 1), dim3(kThreads, 1, 1), args,
-                                    TileShape<BN>::kSmemBytes, stream),
+                                    TileShape<BN, 1>::kSmemBytes, stream),
         "fused_gemm_kernel cooperative launch");
 }
 
@@ -249,6 +278,8 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
     GemmPlan* pl = find_plan(ids[i]);
     if (pl->bn != first->bn || pl->bf16 != first->bf16)
       throw std::runtime_error("tridist_b200: emulated ranks must share the kernel variant");
+    if (pl->cta_m != 1)
+      throw std::runtime_error("tridist_b200: emulated launches use single-CTA tiles (allow_pair = 0)");
     host[i] = pl->prm[parity & 1];
     host[i].round = round;
     host[i].skip_comm = skip_comm;

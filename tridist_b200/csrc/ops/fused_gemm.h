@@ -26,6 +26,7 @@ struct GemmPlanDesc {
   int list_len = 0;
   int swiglu_up_row0 = 0;
   int max_ctas = 0;
+  int allow_pair = 1;   // let 256-wide tiles run on CTA pairs (cluster of 2, cta_group::2 MMA)
   // all-gather
   int64_t peer_ws[2][8] = {};
   int64_t peer_ag_flags[8] = {};

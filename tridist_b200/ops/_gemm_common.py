@@ -86,7 +86,8 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              M=M, N=N, K=K, a=a.data_ptr(), a_rows=a.shape[0], lda=a.stride(0),
              b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
              status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
-             max_ctas=env_int("TRIDIST_MAX_CTAS", 0))
+             max_ctas=env_int("TRIDIST_MAX_CTAS", 0),
+             allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and getattr(world, "kind", "") != "emulated") else 0)
     return d
 
 

@@ -8,6 +8,7 @@ that still mean something on B200 are read here, under the ``TRIDIST_`` prefix.
 TRIDIST_WAIT_TIMEOUT_MS   limit of every in-kernel wait (default 4000)
 TRIDIST_MAX_CTAS          cap on the persistent grid of the fused GEMM kernels
 TRIDIST_FORCE_BN          128 or 256: override the output-tile width heuristic
+TRIDIST_CTA_PAIR          0: never run 256-wide tiles on CTA pairs (2-CTA tcgen05 MMA); default 1
 TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot"
 TRIDIST_AR_ONE_SHOT_BYTES size threshold (bytes of one rank's partial) below which
                           the one-shot all-reduce is used (default 4 MiB)
