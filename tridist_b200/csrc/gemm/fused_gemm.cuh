@@ -108,6 +108,7 @@ struct alignas(64) GemmParams {
   uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
   int32_t chunk_rows, n_chunks, push_parts;
   int32_t skip_comm;
+  int32_t comm_only;
 
   // ---- OP_RS / OP_AR* ----
   void* peer_slots[kMaxRanks];     // slot base (this round's parity) on every rank: [R][rows][N]
@@ -227,6 +228,39 @@ __device__ __forceinline__ void add_row32(float (&acc)[32], const void* src) {
   }
 }
 
+// acc += sum over sources s in [0, R), s != skip, of the 32 16-bit values at
+// base + s * stride_bytes (64 bytes each). Loads of four sources are issued together so
+// that their latencies overlap; the accumulation order is fixed (ascending s).
+template <bool kBf16>
+__device__ __forceinline__ void add_rows32_from_sources(float (&acc)[32], const uint8_t* base,
+                                                        int64_t stride_bytes, int R, int skip) {
+  constexpr int kBatch = 3;
+  for (int s0 = 0; s0 < R; s0 += kBatch) {
+    uint4 v[kBatch][4];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int s = s0 + u;
+      const bool on = s < R && s != skip;
+      const uint4* src = reinterpret_cast<const uint4*>(base + (on ? s : 0) * stride_bytes);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) v[u][q] = on ? ld_global_cg_v4(src + q) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t w[4] = {v[u][q].x, v[u][q].y, v[u][q].z, v[u][q].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<kBf16>(w[j]);   // inactive sources contribute +0.0
+          acc[q * 8 + j * 2] += f.x;
+          acc[q * 8 + j * 2 + 1] += f.y;
+        }
+      }
+    }
+  }
+}
+
 template <bool kBf16>
 __device__ __forceinline__ void store_row32(void* dst, const float (&acc)[32]) {
   uint4* d = reinterpret_cast<uint4*>(dst);
@@ -334,7 +368,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  const int positions = sched_positions(p);
+  // comm_only: no tiles are computed, only the communication warps run (push timing)
+  const int positions = p.comm_only ? 0 : sched_positions(p);
   const WaitEnv env = p.env;
 
   // ==========================================================================
@@ -659,34 +694,26 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             if (owner != p.rank) continue;
             const int lrow = row - owner * p.m_per_rank;
             // fixed source order keeps the sum deterministic
-            for (int s = 0; s < p.R; ++s) {
-              if (s == p.rank) continue;
-              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
-                                    (static_cast<int64_t>(s) * p.slot_stride +
-                                     static_cast<int64_t>(lrow) * p.N + ocol) * 2;
-              add_row32<kBf16>(acc, slot);
-            }
+            add_rows32_from_sources<kBf16>(
+                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                         (static_cast<int64_t>(lrow) * p.N + ocol) * 2,
+                p.slot_stride * 2, p.R, p.rank);
             store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
                                    (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
                                acc);
           } else if (p.op == OP_AR1) {
             const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-            for (int s = 0; s < p.R; ++s) {
-              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
-                                    (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
-              add_row32<kBf16>(acc, slot);
-            }
+            add_rows32_from_sources<kBf16>(
+                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
+                p.slot_stride * 2, p.R, -1);
             store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
                                    (static_cast<int64_t>(row) * ldc + ocol) * 2,
                                acc);
           } else {  // OP_AR2, this rank owns the tile
             const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-            for (int s = 0; s < p.R; ++s) {
-              if (s == p.rank) continue;
-              const uint8_t* slot = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
-                                    (static_cast<int64_t>(s) * p.slot_stride + off) * 2;
-              add_row32<kBf16>(acc, slot);
-            }
+            add_rows32_from_sources<kBf16>(
+                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
+                p.slot_stride * 2, p.R, p.rank);
             uint4* d4 = reinterpret_cast<uint4*>(my_stage + (c & 3) * 64);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -803,15 +830,30 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int rows = min(BM, p.M - mt * BM);
         const int cols = min(BN, p.N - nt * BN);
         const int v_per_row = cols >> 3;
-        for (int idx = ctid; idx < rows * v_per_row; idx += kCommThreads) {
-          const int r = idx / v_per_row;
-          const int v = idx - r * v_per_row;
-          const int64_t off = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
-          const uint4 val =
-              ld_global_cg_v4(reinterpret_cast<const uint8_t*>(p.peer_res[p.rank]) + off * 2);
-          st_global_v4(reinterpret_cast<uint8_t*>(p.c) +
-                           (static_cast<int64_t>(mt * BM + r) * p.ldc + nt * BN + v * 8) * 2,
-                       val);
+        const int total = rows * v_per_row;
+        for (int i0 = ctid; i0 < total; i0 += 8 * kCommThreads) {
+          uint4 val[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = i0 + u * kCommThreads;
+            if (idx < total) {
+              const int r = idx / v_per_row;
+              const int v = idx - r * v_per_row;
+              const int64_t off = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
+              val[u] = ld_global_cg_v4(reinterpret_cast<const uint8_t*>(p.peer_res[p.rank]) + off * 2);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = i0 + u * kCommThreads;
+            if (idx < total) {
+              const int r = idx / v_per_row;
+              const int v = idx - r * v_per_row;
+              st_global_v4(reinterpret_cast<uint8_t*>(p.c) +
+                               (static_cast<int64_t>(mt * BM + r) * p.ldc + nt * BN + v * 8) * 2,
+                           val[u]);
+            }
+          }
         }
       }
     }

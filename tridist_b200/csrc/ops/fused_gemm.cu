@@ -236,7 +236,8 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
   GemmParams& p = plan->prm[parity & 1];
   p.round = round;
   p.order_table = reinterpret_cast<const int32_t*>(order_table);
-  p.skip_comm = skip_comm;
+  p.skip_comm = skip_comm & 1;
+  p.comm_only = (skip_comm >> 1) & 1;
   if (plan->bn == 256) {
     if (plan->cta_m == 2) {
       if (plan->bf16) launch_one<256, true, 2>(p, plan->grid_x, stream);

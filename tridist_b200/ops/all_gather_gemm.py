@@ -157,14 +157,15 @@ def _check_args(a, b, c, ctx):
 
 
 def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[torch.Tensor] = None,
-                          fuse_swiglu: bool = False):
+                          fuse_swiglu: bool = False, comm_only: bool = False):
     """``c[M, N_pr] = allgather_M(a) @ b.T``.
 
     ``skip_comm=True`` is the GEMM-only decomposition mode: the kernel multiplies
     the workspace left by the last full call and pushes nothing.
     ``order_table`` (device int32[R]) overrides the source visiting order for this
     call (skew-aware scheduling). ``fuse_swiglu`` treats b as ``[gate; up]`` and
-    writes ``silu(gate) * up`` (c has N_pr/2 columns).
+    writes ``silu(gate) * up`` (c has N_pr/2 columns). ``comm_only=True`` is the push-only
+    decomposition mode: the shard is pushed and the tickets are raised, no tile is computed.
     """
     if isinstance(ctx.world, CpuWorld):
         return cpu_backend.ag_gemm(a, b, c, ctx, skip_comm, fuse_swiglu)
@@ -178,7 +179,7 @@ def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[t
     pid = _plan(ctx, a, b, c, fuse_swiglu)
     native().gemm_plan_launch(pid, ctx.flag_round, ctx.flag_round & 1,
                               order_table.data_ptr() if order_table is not None else 0,
-                              1 if skip_comm else 0)
+                              (1 if skip_comm else 0) | (2 if comm_only else 0))
     return c
 
 

@@ -39,7 +39,10 @@ def time_op(fn: Callable[[], None], iters: int = 20, warmup: int = 3, flush: boo
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    times = []
+    # All iterations are enqueued back to back and synchronised once, so that host-side
+    # launch latency hides behind the flush / barrier of the same iteration instead of
+    # showing up inside the event interval.
+    pairs = []
     for _ in range(iters):
         if flush:
             flush_l2()
@@ -50,8 +53,9 @@ def time_op(fn: Callable[[], None], iters: int = 20, warmup: int = 3, flush: boo
         e0.record()
         fn()
         e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
+        pairs.append((e0, e1))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) for a, b in pairs]
     times = max_over_ranks(times, group)
     return {"mean": statistics.fmean(times), "p50": statistics.median(times), "min": min(times),
             "iters": iters}
