@@ -188,6 +188,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                : "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// Untiled bulk copy global -> shared of this CTA; completion bytes are credited to `bar`.
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(void* sdst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(sdst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
 // Untiled bulk copy shared -> global (local or peer memory); both addresses 16-byte
 // aligned, size a multiple of 16 bytes. Completion is tracked by the bulk async-group.
 __device__ __forceinline__ void bulk_store_1d(void* gdst, const void* ssrc, uint32_t bytes) {

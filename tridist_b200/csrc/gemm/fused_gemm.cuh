@@ -62,18 +62,21 @@ constexpr int kStageRowBytes = kStageCols * 2;
 constexpr int kStagePitch = kStageRowBytes + 16;
 constexpr int kStagingBytes = BM * kStagePitch;
 
-template <int BN, int kCtaM>
+template <int BN, int kCtaM, bool kStaging>
 struct TileShape {
   // kCtaM = 2: two CTAs (one cluster) share each tcgen05 MMA; a pair owns a 256 x BN
   // output tile, every CTA loads its own 128 rows of A and its own BN/2 rows of B.
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = (BN / kCtaM) * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (192 * 1024) / kStageBytes;
+  // 227 KB per CTA: the epilogue staging is only carved out for the operators whose
+  // epilogue publishes tiles to other ranks; the others get a deeper ring instead.
+  static constexpr int kStagingUsed = kStaging ? kStagingBytes : 0;
+  static constexpr int kStages = (226 * 1024 - kStagingUsed) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;
   // ring + epilogue staging (one padded 256-byte row per accumulator row) + 1 KB for
   // barriers and the TMEM slot; the dynamic shared array is declared 1024-byte aligned
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingUsed + 1024;
 };
 
 struct alignas(64) GemmParams {
@@ -303,10 +306,10 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 // ----------------------------------------------------------------------------
 // The kernel
 // ----------------------------------------------------------------------------
-template <int BN, bool kBf16, int kCtaM>
+template <int BN, bool kBf16, int kCtaM, bool kStaging>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __restrict__ pv) {
-  using TS = TileShape<BN, kCtaM>;
+  using TS = TileShape<BN, kCtaM, kStaging>;
   static_assert(kCtaM == 1 || BN == 256, "CTA pairs are built for 256-wide tiles only");
   // With pv != nullptr the launch emulates several ranks on one GPU: grid.y
   // indexes the rank and each rank reads its own parameter block.
@@ -315,13 +318,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;
   uint8_t* staging = smem + TS::kStages * TS::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TS::kStagingUsed);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + TS::kStages;
   uint64_t* tmem_full_bar = bars + 2 * TS::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* drain_bar = tmem_empty_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* push_bar = drain_bar + 1;            // 2 barriers of the all-gather push ring
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + 2);
   int32_t* s_order = reinterpret_cast<int32_t*>(tmem_slot + 4);
   // s_flags[0]: an epilogue warp gave up; s_flags[1]: outcome of the comm warps' last wait
   volatile int32_t* s_flags = s_order + kMaxRanks;
@@ -345,6 +349,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       mbar_init(&tmem_empty_bar[b], 4 * kCtaM);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(&push_bar[0], 1);
+    mbar_init(&push_bar[1], 1);
     s_flags[0] = 0;
     s_flags[1] = 1;
     mbar_fence_init();
@@ -580,7 +586,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // ---- phase 1: publish 16-bit partials into other ranks' slots --------------
       // Always before any wait: two owners of one mixed tile would otherwise wait
       // for each other's partial.
-      if (tile_publishes) {
+      if (kStaging && tile_publishes) {
         // Each thread owns one accumulator row: it converts 128 columns into its staging
         // row, then ships the 256 contiguous bytes to every destination with one bulk
         // copy each (large NVLink writes instead of scattered 16-byte stores).
@@ -656,7 +662,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool finalizes =
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
-        const bool bcast = multi && p.op == OP_AR2;   // reduced tile goes out through staging
+        const bool bcast = kStaging && multi && p.op == OP_AR2;   // reduced tile goes out via staging
         uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
         for (int c = 0; c < BN / 32; ++c) {
           if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
@@ -766,38 +772,58 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // ==========================================================================
   else {
     const int ctid = threadIdx.x - kCommWarp0 * 32;
-    if (p.op == OP_AG && p.R > 1 && !p.skip_comm) {
-      // Push this rank's shard to every peer, nearest-next rank first, so that
-      // at any moment each rank receives from exactly one sender. One work item
-      // is one `part` of one chunk for one destination.
-      const int64_t chunk_bytes = static_cast<int64_t>(p.chunk_rows) * p.K * 2;
-      const int64_t part_bytes = chunk_bytes / p.push_parts;   // host guarantees % 16 == 0
-      const int items_per_dest = p.n_chunks * p.push_parts;
-      const int items = (p.R - 1) * items_per_dest;
-      const int gx = gridDim.x;
-      for (int item = blockIdx.x; item < items; item += gx) {
-        const int di = item / items_per_dest;
-        const int rem = item - di * items_per_dest;
-        const int ck = rem / p.push_parts;
-        const int part = rem - ck * p.push_parts;
-        const int dest = (p.rank + 1 + di) % p.R;
-        const int64_t src_off = ck * chunk_bytes + part * part_bytes;
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a_local) + src_off;
-        uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_ws[dest]) +
-                       static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2 + src_off;
-        const int64_t n16 = part_bytes >> 4;
-        int64_t i = ctid;
-        for (; i + 7 * kCommThreads < n16; i += 8 * kCommThreads) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = ld_global_nc_v4(src + ((i + u * kCommThreads) << 4));
-#pragma unroll
-          for (int u = 0; u < 8; ++u) st_global_v4(dst + ((i + u * kCommThreads) << 4), v[u]);
-        }
-        for (; i < n16; i += kCommThreads) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
-        fence_acq_rel_sys();
-        named_bar_sync(1, kCommThreads);
-        if (ctid == 0) {
+    if (kStaging && p.op == OP_AG && p.R > 1 && !p.skip_comm) {
+      // Push this rank's shard to every peer, nearest-next rank first, so that at any
+      // moment each rank receives from exactly one sender. One work item is one `part`
+      // of one chunk for one destination. A single thread drives the copy engine of
+      // the SM: 16 KB pieces are bulk-loaded into a two-slot shared-memory ring and
+      // bulk-stored to the peer, so the push costs no load/store-unit bandwidth and
+      // NVLink sees large writes.
+      if (ctid == 0) {
+        constexpr uint32_t kPiece = 16384;
+        const int64_t chunk_bytes = static_cast<int64_t>(p.chunk_rows) * p.K * 2;
+        const int64_t part_bytes = chunk_bytes / p.push_parts;   // host guarantees % 16 == 0
+        const int items_per_dest = p.n_chunks * p.push_parts;
+        const int items = (p.R - 1) * items_per_dest;
+        const int pieces = static_cast<int>((part_bytes + kPiece - 1) / kPiece);
+        uint32_t par[2] = {0u, 0u};
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+          const int di = item / items_per_dest;
+          const int rem = item - di * items_per_dest;
+          const int ck = rem / p.push_parts;
+          const int part = rem - ck * p.push_parts;
+          const int dest = (p.rank + 1 + di) % p.R;
+          const int64_t src_off = ck * chunk_bytes + part * part_bytes;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a_local) + src_off;
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_ws[dest]) +
+                         static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2 + src_off;
+          auto piece_bytes = [&](int i) -> uint32_t {
+            const int64_t left = part_bytes - static_cast<int64_t>(i) * kPiece;
+            return static_cast<uint32_t>(left < kPiece ? left : kPiece);
+          };
+          // prologue: piece 0 into slot 0 (all earlier stores were drained at the end of
+          // the previous item)
+          mbar_arrive_expect_tx(&push_bar[0], piece_bytes(0));
+          bulk_load_1d(staging, src, piece_bytes(0), &push_bar[0]);
+          for (int i = 0; ok && i < pieces; ++i) {
+            const int b = i & 1;
+            if (i + 1 < pieces) {
+              // slot b^1 was read by the store of piece i-1: let that read finish first
+              tma_store_wait_read<0>();
+              mbar_arrive_expect_tx(&push_bar[b ^ 1], piece_bytes(i + 1));
+              bulk_load_1d(staging + (b ^ 1) * kPiece, src + static_cast<int64_t>(i + 1) * kPiece,
+                           piece_bytes(i + 1), &push_bar[b ^ 1]);
+            }
+            ok = wait_mbar(&push_bar[b], par[b], env, SITE_PIPE_FULL, 100 + b);
+            par[b] ^= 1u;
+            if (!ok) break;
+            bulk_store_1d(dst + static_cast<int64_t>(i) * kPiece, staging + b * kPiece, piece_bytes(i));
+            tma_store_commit();
+          }
+          tma_store_wait_all<0>();             // every byte of the item has been written
+          if (!ok) break;
+          fence_acq_rel_sys();
           uint32_t* cnt = p.ag_counters + dest * p.n_chunks + ck;
           const uint32_t old = atomicAdd(cnt, 1u);
           if (old + 1u == static_cast<uint32_t>(p.push_parts)) {

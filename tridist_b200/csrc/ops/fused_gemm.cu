@@ -88,13 +88,13 @@ static int num_sms() {
   return n;
 }
 
-template <int BN, bool kBf16, int kCtaM>
+template <int BN, bool kBf16, int kCtaM, bool kStaging>
 static void set_attr_once() {
   static bool done = false;
   if (!done) {
-    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16, kCtaM>,
+    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16, kCtaM, kStaging>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               TileShape<BN, kCtaM>::kSmemBytes),
+                               TileShape<BN, kCtaM, kStaging>::kSmemBytes),
           "cudaFuncSetAttribute(smem)");
     done = true;
   }
@@ -209,13 +209,13 @@ static GemmPlan* find_plan(int64_t id) {
   return it->second;
 }
 
-template <int BN, bool kBf16, int kCtaM>
+template <int BN, bool kBf16, int kCtaM, bool kStaging>
 static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
-  set_attr_once<BN, kBf16, kCtaM>();
+  set_attr_once<BN, kBf16, kCtaM, kStaging>();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid_x, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = TileShape<BN, kCtaM>::kSmemBytes;
+  cfg.dynamicSmemBytes = TileShape<BN, kCtaM, kStaging>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -225,7 +225,7 @@ static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const GemmParams* none = nullptr;
-  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM>, p, none),
+  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM, kStaging>, p, none),
         "fused_gemm_kernel launch");
 }
 
@@ -238,32 +238,39 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
   p.order_table = reinterpret_cast<const int32_t*>(order_table);
   p.skip_comm = skip_comm & 1;
   p.comm_only = (skip_comm >> 1) & 1;
+  // operators that ship data to other ranks (epilogue tiles, all-gather push) need the staging area
+  const bool staging = p.R > 1 && (p.op == OP_RS || p.op == OP_AR1 || p.op == OP_AR2 || p.op == OP_AG);
+#define TDB_LAUNCH(BN_, PAIR_)                                                              \
+  do {                                                                                      \
+    if (plan->bf16) {                                                                       \
+      if (staging) launch_one<BN_, true, PAIR_, true>(p, plan->grid_x, stream);             \
+      else launch_one<BN_, true, PAIR_, false>(p, plan->grid_x, stream);                    \
+    } else {                                                                                \
+      if (staging) launch_one<BN_, false, PAIR_, true>(p, plan->grid_x, stream);            \
+      else launch_one<BN_, false, PAIR_, false>(p, plan->grid_x, stream);                   \
+    }                                                                                       \
+  } while (0)
   if (plan->bn == 256) {
-    if (plan->cta_m == 2) {
-      if (plan->bf16) launch_one<256, true, 2>(p, plan->grid_x, stream);
-      else launch_one<256, false, 2>(p, plan->grid_x, stream);
-    } else {
-      if (plan->bf16) launch_one<256, true, 1>(p, plan->grid_x, stream);
-      else launch_one<256, false, 1>(p, plan->grid_x, stream);
-    }
+    if (plan->cta_m == 2) TDB_LAUNCH(256, 2);
+    else TDB_LAUNCH(256, 1);
   } else {
-    if (plan->bf16) launch_one<128, true, 1>(p, plan->grid_x, stream);
-    else launch_one<128, false, 1>(p, plan->grid_x, stream);
+    TDB_LAUNCH(128, 1);
   }
+#undef TDB_LAUNCH
   ++g_launches;
 }
 
 template <int BN, bool kBf16>
 static void launch_emulated(const GemmParams* dev, int grid_x, int vranks, cudaStream_t stream) {
-  set_attr_once<BN, kBf16, 1>();
+  set_attr_once<BN, kBf16, 1, true>();
   GemmParams dummy;
   std::memset(&dummy, 0, sizeof(dummy));
   void* args[2] = {&dummy, &dev};
   // Cooperative launch: the runtime refuses the launch unless every CTA of
   // every emulated rank can be resident at once, which the cross-rank waits need.
-  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1>),
+  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1, true>),
                                     dim3(grid_x, vranks, 1), dim3(kThreads, 1, 1), args,
-                                    TileShape<BN, 1>::kSmemBytes, stream),
+                                    TileShape<BN, 1, true>::kSmemBytes, stream),
         "fused_gemm_kernel cooperative launch");
 }
 
