@@ -63,6 +63,17 @@ def main():
     def t(fn):
         return round(time_op(fn, iters=args.iters, warmup=3, flush=True, barrier=rt.barrier_on_stream)["p50"], 4)
 
+    def prof_of(fn):
+        """One more call with the stall accounting read back (only with TRIDIST_PROF=1)."""
+        from tridist_b200.ops._gemm_common import prof_buffer, read_prof
+        if prof_buffer() is None:
+            return None
+        prof_buffer().zero_()
+        rt.barrier_on_stream()
+        fn()
+        torch.cuda.synchronize()
+        return read_prof()
+
     def emit(name, cell):
         results[name] = cell
         if rank == 0:
@@ -102,6 +113,10 @@ def main():
             if R > 1:
                 cell["nccl_only"] = t(lambda: dist.all_gather_into_tensor(base.full, a))
                 cell["fused_push_only"] = t(lambda: ag_gemm_intra_node_op(a, b, c, ctx, comm_only=True))
+            pr = prof_of(lambda: ag_gemm_intra_node_op(a, b, c, ctx))
+            if pr:
+                cell["prof_us"] = pr
+                cell["prof_gemm_only_us"] = prof_of(lambda: ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=True))
             emit(name, cell)
             rt.check(sync=True)
 
@@ -126,6 +141,9 @@ def main():
                     "roofline": round(roofline.gemm_rs_roof(M, N, kl, R)["ms"], 4), "err": err}
             if R > 1:
                 cell["nccl_only"] = t(lambda: dist.reduce_scatter_tensor(base.out, base.partial))
+            pr = prof_of(lambda: gemm_rs_intra_node_op(a, b, dt, rank, R, ctx, out=out))
+            if pr:
+                cell["prof_us"] = pr
             emit(name, cell)
             rt.check(sync=True)
 
@@ -154,6 +172,9 @@ def main():
                 cell["fused_two_shot_symm_c"] = t(lambda: gemm_ar_intra_node_op(a, b, ctx.symm_output(M), ctx))
                 del cs
                 cell["nccl_only"] = t(lambda: dist.all_reduce(base.c))
+            pr = prof_of(lambda: gemm_ar_intra_node_op(a, b, c, ctx))
+            if pr:
+                cell["prof_us_" + ctx.mode] = pr
             cell["fused_gemm_only"] = t(lambda: gemm_ar_intra_node_op(a, b, c, ctx, component="gemm"))
             cell["cublas_nccl"] = t(lambda: base(a, b))
             cell["cublas_only"] = t(lambda: torch.matmul(a, b.t(), out=base.c))

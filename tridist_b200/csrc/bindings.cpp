@@ -72,12 +72,14 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   g.n_chunks = get<int>(d, "n_chunks", 0);
   g.push_parts = get<int>(d, "push_parts", 0);
   g.skip_comm = get<int>(d, "skip_comm", 0);
+  g.push_ctas = get<int>(d, "push_ctas", 0);
   fill_ptrs2(d, "peer_slots", g.peer_slots);
   fill_ptrs(d, "peer_tile_flags", g.peer_tile_flags, 8);
   g.slot_stride = get<int64_t>(d, "slot_stride", 0);
   fill_ptrs2(d, "peer_res", g.peer_res);
   fill_ptrs(d, "peer_res_flags", g.peer_res_flags, 8);
   g.res_is_c = get<int>(d, "res_is_c", 0);
+  g.prof = get<int64_t>(d, "prof", 0);
   g.status_dev = get<int64_t>(d, "status_dev", 0);
   g.abort_word = get<int64_t>(d, "abort_word", 0);
   g.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);

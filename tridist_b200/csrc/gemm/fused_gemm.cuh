@@ -79,6 +79,21 @@ struct TileShape {
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingUsed + 1024;
 };
 
+// Per-CTA stall accounting slots (nanoseconds unless noted).
+enum ProfSlot : int {
+  PROF_LOAD_FLAG_WAIT = 0,   // TMA warp: waiting for all-gather tickets
+  PROF_LOAD_EMPTY_WAIT = 1,  // TMA warp: waiting for a free smem stage
+  PROF_MMA_FULL_WAIT = 2,    // MMA warp: waiting for operands (starved)
+  PROF_MMA_TMEM_WAIT = 3,    // MMA warp: waiting for the epilogue to drain an accumulator
+  PROF_EPI_BUSY = 4,         // epilogue: accumulator ready -> accumulator released
+  PROF_EPI_PUBLISH = 5,      // epilogue: phase 1 (ship partials, wait for the writes, ticket)
+  PROF_EPI_TICKET_WAIT = 6,  // epilogue: phase 2 (waiting for other ranks' partials)
+  PROF_EPI_TILES = 7,        // epilogue: tiles processed (count)
+  PROF_PUSH_TOTAL = 8,       // communication warps: whole push / collect loop
+  PROF_KERNEL = 9,           // CTA lifetime
+  kProfSlots = 16,
+};
+
 struct alignas(64) GemmParams {
   CUtensorMap tma_a;       // A [rows, K]; for OP_AG this rank's local shard [M_pr, K]
   CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
@@ -112,6 +127,7 @@ struct alignas(64) GemmParams {
   int32_t chunk_rows, n_chunks, push_parts;
   int32_t skip_comm;
   int32_t comm_only;
+  int32_t push_ctas;       // CTAs that take part in the all-gather push (0 = all)
 
   // ---- OP_RS / OP_AR* ----
   void* peer_slots[kMaxRanks];     // slot base (this round's parity) on every rank: [R][rows][N]
@@ -120,6 +136,10 @@ struct alignas(64) GemmParams {
   void* peer_res[kMaxRanks];       // OP_AR2: reduced-result buffer [M][N] on every rank
   uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [tiles] tickets
   int32_t res_is_c;                // OP_AR2: caller's c aliases peer_res[rank]; skip the copy
+
+  // Optional stall accounting: [gridDim.x][kProfSlots] nanosecond sums written at kernel end
+  // (see ProfSlot); nullptr = off, no timer is read.
+  uint64_t* prof;
 
   WaitEnv env;
   int32_t pad_[2];
@@ -377,6 +397,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // comm_only: no tiles are computed, only the communication warps run (push timing)
   const int positions = p.comm_only ? 0 : sched_positions(p);
   const WaitEnv env = p.env;
+  uint64_t* const prof = p.prof ? p.prof + static_cast<int64_t>(blockIdx.x) * kProfSlots : nullptr;
+  const uint64_t t_kernel0 = prof ? globaltimer_ns() : 0;
 
   // ==========================================================================
   // warp 0: TMA producer
@@ -387,6 +409,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       tma_prefetch_desc(&p.tma_b);
       if (p.op == OP_AG) tma_prefetch_desc(&p.tma_a_ws);
       uint32_t stage = 0, phase = 0;
+      uint64_t acc_a = 0, acc_b = 0;
       uint32_t ready_mask[kMaxRanks] = {0};   // chunks of each source already observed
       uint32_t pending = 0;                   // stages with a load in flight (bitmask)
       bool ok = true;
@@ -410,7 +433,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               for (int ck = r_lo / p.chunk_rows; ok && ck <= r_hi / p.chunk_rows; ++ck) {
                 if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
                 const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.n_chunks + ck;
+                const uint64_t tw = prof ? globaltimer_ns() : 0;
                 ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck);
+                if (prof) acc_a += globaltimer_ns() - tw;
                 if (ok) {
                   if (ck < 32) ready_mask[src] |= 1u << ck;
                   if (p.arrival_ns != nullptr && ck == 0)
@@ -426,7 +451,13 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           }
         }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
+          if (prof && !mbar_try_wait(&empty_bar[stage], phase ^ 1u)) {
+            const uint64_t tw = globaltimer_ns();
+            ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
+            acc_b += globaltimer_ns() - tw;
+          } else {
+            ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
+          }
           if (!ok) break;
           pending &= ~(1u << stage);
           uint8_t* sa = ring + stage * TS::kStageBytes;
@@ -458,6 +489,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      if (prof) {
+        prof[PROF_LOAD_FLAG_WAIT] = acc_a;
+        prof[PROF_LOAD_EMPTY_WAIT] = acc_b;
+      }
       if (!ok) {
         // Unwinding: let the loads already issued land before the CTA's shared
         // memory is released (each such wait is itself bounded).
@@ -481,6 +516,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = umma_idesc_f16(kBf16, BM * kCtaM, BN);
       uint32_t stage = 0, phase = 0;
+      uint64_t acc_f = 0, acc_t = 0;
       int it = 0;
       bool ok = true;
       for (int pos = unit0; ok && pos < positions; pos += unit_stride) {
@@ -488,12 +524,24 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (!t.valid) continue;
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
-        ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
+        if (prof && !mbar_try_wait(&tmem_empty_bar[buf], (use & 1u) ^ 1u)) {
+          const uint64_t tw = globaltimer_ns();
+          ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
+          acc_t += globaltimer_ns() - tw;
+        } else {
+          ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
+        }
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
+          if (prof && !mbar_try_wait(&full_bar[stage], phase)) {
+            const uint64_t tw = globaltimer_ns();
+            ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
+            acc_f += globaltimer_ns() - tw;
+          } else {
+            ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
+          }
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(ring + stage * TS::kStageBytes);
@@ -521,6 +569,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         else umma_commit(&tmem_full_bar[buf]);
         ++it;
       }
+      if (prof) {
+        prof[PROF_MMA_FULL_WAIT] = acc_f;
+        prof[PROF_MMA_TMEM_WAIT] = acc_t;
+      }
       if (!ok) {
         // Unwinding: MMAs already issued must retire before TMEM is freed.
         if constexpr (kCtaM == 2) umma_commit_pair_local(drain_bar);
@@ -541,6 +593,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     const int64_t ldc = p.ldc;
     const int tiles = p.unit_m * p.cta_m * p.n_tiles;   // ticket words per source
     const bool multi = p.R > 1;
+    uint64_t acc_busy = 0, acc_pub = 0, acc_tick = 0, n_tiles_done = 0;
     int it = 0;
     for (int pos = unit0; pos < positions; pos += unit_stride) {
       const TileCoord t = tile_at(p, s_order, pos, sub);
@@ -553,6 +606,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                     wait_mbar(&tmem_full_bar[buf], use & 1u, env, SITE_TMEM_FULL, buf)))
         break;
       tc_fence_after_sync();
+      const uint64_t t_epi0 = (prof && etid == 0) ? globaltimer_ns() : 0;
 
       const int row = t.m_tile * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -586,6 +640,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // ---- phase 1: publish 16-bit partials into other ranks' slots --------------
       // Always before any wait: two owners of one mixed tile would otherwise wait
       // for each other's partial.
+      const uint64_t t_pub0 = (prof && etid == 0) ? globaltimer_ns() : 0;
       if (kStaging && tile_publishes) {
         // Each thread owns one accumulator row: it converts 128 columns into its staging
         // row, then ships the 256 contiguous bytes to every destination with one bulk
@@ -644,6 +699,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         }
       }
 
+      const uint64_t t_pub1 = (prof && etid == 0) ? globaltimer_ns() : 0;
       // ---- phase 2: wait for the other sources' partials of this tile -------------
       if (tile_reduces) {
         bool ok = true;
@@ -658,6 +714,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (!epi_vote(&s_flags[0], ok)) break;
       }
 
+      if (prof && etid == 0) {
+        acc_pub += t_pub1 - t_pub0;
+        acc_tick += globaltimer_ns() - t_pub1;
+      }
       // ---- phase 3: final values of the rows / tile this rank keeps ---------------
       const bool finalizes =
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
@@ -757,6 +817,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if constexpr (kCtaM == 2) mbar_arrive_leader(&tmem_empty_bar[buf]);
         else mbar_arrive(&tmem_empty_bar[buf]);
       }
+      if (prof && etid == 0) {
+        acc_busy += globaltimer_ns() - t_epi0;
+        ++n_tiles_done;
+      }
 
       // ---- two-shot: tell every rank the reduced tile is in its result buffer ------
       if (multi && p.op == OP_AR2 && tile_reduces) {
@@ -765,6 +829,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (etid < p.R && etid != p.rank) st_release_sys(p.peer_res_flags[etid] + t.linear, p.round);
       }
       ++it;
+    }
+    if (prof && etid == 0) {
+      prof[PROF_EPI_BUSY] = acc_busy;
+      prof[PROF_EPI_PUBLISH] = acc_pub;
+      prof[PROF_EPI_TICKET_WAIT] = acc_tick;
+      prof[PROF_EPI_TILES] = n_tiles_done;
     }
   }
   // ==========================================================================
@@ -788,7 +858,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int pieces = static_cast<int>((part_bytes + kPiece - 1) / kPiece);
         uint32_t par[2] = {0u, 0u};
         bool ok = true;
-        for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+        const int pushers = (p.push_ctas > 0 && p.push_ctas < static_cast<int>(gridDim.x))
+                                ? p.push_ctas : static_cast<int>(gridDim.x);
+        for (int item = blockIdx.x; ok && blockIdx.x < pushers && item < items; item += pushers) {
           const int di = item / items_per_dest;
           const int rem = item - di * items_per_dest;
           const int ck = rem / p.push_parts;
@@ -885,6 +957,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     }
   }
 
+  if (prof && threadIdx.x == kCommWarp0 * 32)
+    prof[PROF_PUSH_TOTAL] = globaltimer_ns() - (p.prof ? t_kernel0 : 0);
   // ==========================================================================
   // teardown
   // ==========================================================================
@@ -898,6 +972,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     if constexpr (kCtaM == 2) tmem_dealloc_pair(tmem_base, TS::kTmemCols);
     else tmem_dealloc(tmem_base, TS::kTmemCols);
   }
+  if (prof && threadIdx.x == 0) prof[PROF_KERNEL] = globaltimer_ns() - t_kernel0;
 }
 
 }  // namespace tdb

@@ -153,6 +153,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.n_chunks = d.n_chunks > 0 ? d.n_chunks : 1;
     p.push_parts = d.push_parts > 0 ? d.push_parts : 1;
     p.skip_comm = d.skip_comm;
+    p.push_ctas = d.push_ctas;
     p.ag_counters = reinterpret_cast<uint32_t*>(d.ag_counters);
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
@@ -170,6 +171,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
         throw std::runtime_error("tridist_b200: AG push part size must be a multiple of 16 bytes");
       p.tma_a_ws = make_tmap(p.peer_ws[d.rank], d.M, d.K, d.K, d.bf16);
     }
+    p.prof = reinterpret_cast<uint64_t*>(d.prof);
     p.env.status = reinterpret_cast<StatusBlock*>(d.status_dev);
     p.env.abort_word = reinterpret_cast<uint32_t*>(d.abort_word);
     p.env.timeout_ns = d.timeout_ns;

@@ -79,6 +79,36 @@ class PlanCache:
         self._d.clear()
 
 
+PROF_SLOTS = ["load_flag_wait", "load_empty_wait", "mma_full_wait", "mma_tmem_wait", "epi_busy", "epi_publish",
+              "epi_ticket_wait", "epi_tiles", "comm_total", "kernel"]
+_prof_buf: Optional[torch.Tensor] = None
+
+
+def prof_buffer() -> Optional[torch.Tensor]:
+    """Stall-accounting plane of the fused GEMM kernels ([CTA][16] int64 ns sums), allocated when
+    ``TRIDIST_PROF=1``; plans created afterwards write into it."""
+    global _prof_buf
+    if not env_int("TRIDIST_PROF", 0):
+        return None
+    if _prof_buf is None:
+        _prof_buf = torch.zeros((256, 16), dtype=torch.int64, device="cuda")
+    return _prof_buf
+
+
+def read_prof(n_ctas: int = 148) -> Dict[str, Dict[str, float]]:
+    """Mean and max over CTAs of every accounting slot of the LAST kernel, in microseconds
+    (``epi_tiles`` is a count). Call after a synchronisation."""
+    if _prof_buf is None:
+        return {}
+    t = _prof_buf[:n_ctas].cpu().double()
+    out = {}
+    for i, name in enumerate(PROF_SLOTS):
+        col = t[:, i]
+        scale = 1.0 if name == "epi_tiles" else 1e-3
+        out[name] = {"mean": round(float(col.mean()) * scale, 2), "max": round(float(col.max()) * scale, 2)}
+    return out
+
+
 def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr: int, ldc: int,
               M: int, N: int, K: int, bn: int, op: int) -> Dict:
     assert a.stride(1) == 1 and b.stride(1) == 1, "operands must be row-major with unit inner stride"
@@ -87,6 +117,7 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
              status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
              max_ctas=env_int("TRIDIST_MAX_CTAS", 0),
+             prof=(prof_buffer().data_ptr() if prof_buffer() is not None else 0),
              allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and getattr(world, "kind", "") != "emulated") else 0)
     return d
 

@@ -28,6 +28,7 @@ import torch
 from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
+from ..utils.config import env_int
 from ._gemm_common import (BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
                            base_desc, choose_bn, rotation_order)
 
@@ -138,6 +139,7 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["chunk_rows"] = chunk
             d["n_chunks"] = m_pr // chunk
             d["push_parts"] = _push_parts(chunk)
+            d["push_ctas"] = env_int("TRIDIST_PUSH_CTAS", 0)
         return native().gemm_plan_create(d)
 
     return ctx.plans.get(key, make)

@@ -25,7 +25,8 @@ def free_port() -> int:
     return port
 
 
-def _entry(rank: int, world_size: int, backend: str, port: int, fn: Callable, args: tuple, errq):
+def _entry(rank: int, world_size: int, backend: str, port: int, fn: Callable, args: tuple, errq,
+           pg_timeout_s: float = 1800.0):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -35,7 +36,9 @@ def _entry(rank: int, world_size: int, backend: str, port: int, fn: Callable, ar
         if backend == "nccl":
             torch.cuda.set_device(rank)
             kwargs["device_id"] = torch.device("cuda", rank)
-        dist.init_process_group(backend=backend, rank=rank, world_size=world_size, **kwargs)
+        import datetime
+        dist.init_process_group(backend=backend, rank=rank, world_size=world_size,
+                                timeout=datetime.timedelta(seconds=pg_timeout_s), **kwargs)
         fn(rank, world_size, *args)
         dist.barrier()
         dist.destroy_process_group()
@@ -44,7 +47,8 @@ def _entry(rank: int, world_size: int, backend: str, port: int, fn: Callable, ar
         raise
 
 
-def spawn(fn: Callable, world_size: int, backend: str = "gloo", args: tuple = (), timeout: float = 300.0):
+def spawn(fn: Callable, world_size: int, backend: str = "gloo", args: tuple = (), timeout: float = 300.0,
+          pg_timeout_s: float = 1800.0):
     """Run ``fn(rank, world_size, *args)`` in ``world_size`` processes with an initialised
     process group on 127.0.0.1; raises with the first failing rank's traceback."""
     ctx = mp.get_context("spawn")
@@ -52,7 +56,7 @@ def spawn(fn: Callable, world_size: int, backend: str = "gloo", args: tuple = ()
     port = free_port()
     procs = []
     for r in range(world_size):
-        p = ctx.Process(target=_entry, args=(r, world_size, backend, port, fn, args, errq))
+        p = ctx.Process(target=_entry, args=(r, world_size, backend, port, fn, args, errq, pg_timeout_s))
         p.start()
         procs.append(p)
     failed = False
