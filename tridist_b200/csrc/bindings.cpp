@@ -73,6 +73,7 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   g.push_parts = get<int>(d, "push_parts", 0);
   g.skip_comm = get<int>(d, "skip_comm", 0);
   g.push_ctas = get<int>(d, "push_ctas", 0);
+  g.push_skip_rounds = get<int>(d, "push_skip_rounds", 0);
   fill_ptrs2(d, "peer_slots", g.peer_slots);
   fill_ptrs(d, "peer_tile_flags", g.peer_tile_flags, 8);
   g.slot_stride = get<int64_t>(d, "slot_stride", 0);

@@ -98,6 +98,10 @@ struct alignas(64) GemmParams {
   CUtensorMap tma_a;       // A [rows, K]; for OP_AG this rank's local shard [M_pr, K]
   CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
   CUtensorMap tma_b;       // B [N_rows, K], box 128 rows
+  // Store maps (box 128 rows x 64 columns, 128-byte swizzle) over this rank's slot inside
+  // every rank's slot buffer, and over every rank's reduced-result buffer (two-shot).
+  CUtensorMap tma_slot[kMaxRanks];
+  CUtensorMap tma_res[kMaxRanks];
 
   int32_t M, N, K;         // output is M x N (for EPI_SWIGLU: M x N with B holding 2N rows)
   int32_t m_tiles, n_tiles, k_blocks;
@@ -128,6 +132,7 @@ struct alignas(64) GemmParams {
   int32_t skip_comm;
   int32_t comm_only;
   int32_t push_ctas;       // CTAs that take part in the all-gather push (0 = all)
+  int32_t push_skip_rounds;  // scheduling rounds the pushing CTAs sit out
 
   // ---- OP_RS / OP_AR* ----
   void* peer_slots[kMaxRanks];     // slot base (this round's parity) on every rank: [R][rows][N]
@@ -310,6 +315,25 @@ __device__ __forceinline__ void round_row32(float (&acc)[32]) {
   }
 }
 
+// Epilogue staging in the layout a 128-byte-swizzled TMA store expects: two boxes of
+// [128 rows x 64 columns]; inside a box row r occupies 128 bytes and its 16-byte chunk c
+// sits at chunk position c ^ (r & 7). `cc` selects the 32-column quarter of the 128 staged
+// columns.
+template <bool kBf16>
+__device__ __forceinline__ void stage_row32_swizzled(uint8_t* staging, int r, int cc, const float (&acc)[32]) {
+  uint8_t* box_row = staging + (cc >> 1) * (BM * 128) + r * 128;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint4 o;
+    o.x = pack2<kBf16>(acc[v * 8 + 0], acc[v * 8 + 1]);
+    o.y = pack2<kBf16>(acc[v * 8 + 2], acc[v * 8 + 3]);
+    o.z = pack2<kBf16>(acc[v * 8 + 4], acc[v * 8 + 5]);
+    o.w = pack2<kBf16>(acc[v * 8 + 6], acc[v * 8 + 7]);
+    const int chunk = ((cc & 1) * 4 + v) ^ (r & 7);
+    *reinterpret_cast<uint4*>(box_row + chunk * 16) = o;
+  }
+}
+
 // Collective decision of the four epilogue warps. The flag is sticky; the
 // second barrier keeps a fast warp from raising it for a later check while a
 // slow warp has not read it yet, so all 128 threads always agree.
@@ -356,8 +380,24 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // TMEM-empty barriers the pair synchronises on).
   const int sub = (kCtaM == 2) ? static_cast<int>(cluster_ctarank()) : 0;
   const bool leader = sub == 0;
-  const int unit0 = static_cast<int>(blockIdx.x) / kCtaM;
-  const int unit_stride = static_cast<int>(gridDim.x) / kCtaM;
+  // Static round-robin over scheduling positions, with one twist: the CTAs that push the
+  // all-gather shard sit out the first `push_skip_rounds` rounds (their copy engine is busy
+  // and their operand loads are slower meanwhile), so that all CTAs finish together.
+  const int sched_workers = static_cast<int>(gridDim.x) / kCtaM;
+  const int my_worker = static_cast<int>(blockIdx.x) / kCtaM;
+  int sched_pushers = 0, sched_skip = 0;
+  if (p.op == OP_AG && p.R > 1 && !p.skip_comm && p.push_ctas > 0 &&
+      p.push_ctas < static_cast<int>(gridDim.x)) {
+    sched_pushers = (p.push_ctas + kCtaM - 1) / kCtaM;
+    sched_skip = p.push_skip_rounds;
+  }
+  const int sched_early = sched_workers - sched_pushers;    // workers active in the early rounds
+  const bool i_push = my_worker < sched_pushers;
+  auto pos_of = [&](int i) -> int {
+    if (i_push) return sched_skip * sched_early + i * sched_workers + my_worker;
+    if (i < sched_skip) return i * sched_early + (my_worker - sched_pushers);
+    return sched_skip * sched_early + (i - sched_skip) * sched_workers + my_worker;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TS::kStages; ++s) {
@@ -413,7 +453,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       uint32_t ready_mask[kMaxRanks] = {0};   // chunks of each source already observed
       uint32_t pending = 0;                   // stages with a load in flight (bitmask)
       bool ok = true;
-      for (int pos = unit0; ok && pos < positions; pos += unit_stride) {
+      for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
         const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
         const int m0 = t.m_tile * BM;
@@ -519,7 +559,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       uint64_t acc_f = 0, acc_t = 0;
       int it = 0;
       bool ok = true;
-      for (int pos = unit0; ok && pos < positions; pos += unit_stride) {
+      for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
         const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
         const int buf = it & 1;
@@ -595,7 +635,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     const bool multi = p.R > 1;
     uint64_t acc_busy = 0, acc_pub = 0, acc_tick = 0, n_tiles_done = 0;
     int it = 0;
-    for (int pos = unit0; pos < positions; pos += unit_stride) {
+    for (int si = 0, pos = pos_of(0); pos < positions; pos = pos_of(++si)) {
       const TileCoord t = tile_at(p, s_order, pos, sub);
       if (!t.valid) continue;
       const int buf = it & 1;
@@ -642,49 +682,90 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // for each other's partial.
       const uint64_t t_pub0 = (prof && etid == 0) ? globaltimer_ns() : 0;
       if (kStaging && tile_publishes) {
-        // Each thread owns one accumulator row: it converts 128 columns into its staging
-        // row, then ships the 256 contiguous bytes to every destination with one bulk
-        // copy each (large NVLink writes instead of scattered 16-byte stores).
-        uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
-        for (int half = 0; half < BN / kStageCols; ++half) {
-          const int col0 = t.n_tile * BN + half * kStageCols;
-          tma_store_wait_read<0>();          // my previous copies have read this row
+        const bool one_dest_tile = (p.op != OP_RS) || (o_lo == o_hi);
+        if (one_dest_tile) {
+          // The whole tile goes to one rank (or, one-shot, to all of them): stage 128 columns
+          // at a time in TMA layout and let one thread ship them with 2-D tiled stores
+          // (two 128 x 64 boxes per destination) -- few large copy-engine operations.
+          const int r_in_tile = q * 32 + lane;
+          const int dest = (p.op == OP_RS) ? o_lo : owner;      // uniform over the CTA
+          const int row0 = (p.op == OP_RS) ? t.m_tile * BM - dest * p.m_per_rank : t.m_tile * BM;
+          for (int half = 0; half < BN / kStageCols; ++half) {
+            const int col0 = t.n_tile * BN + half * kStageCols;
+            if (col0 >= p.N) break;
+            if (etid == 0) tma_store_wait_read<0>();   // earlier stores have read the staging
+            named_bar_sync(2, kEpiThreads);
 #pragma unroll 1
-          for (int c = 0; c < kStageCols / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(taddr + half * kStageCols + c * 32, r);
-            tmem_ld_wait();
-            uint4* d4 = reinterpret_cast<uint4*>(my_stage + c * 64);
+            for (int c = 0; c < kStageCols / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(taddr + half * kStageCols + c * 32, r);
+              tmem_ld_wait();
+              float acc[32];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o;
-              o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              d4[v] = o;
+              for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
+              stage_row32_swizzled<kBf16>(staging, r_in_tile, c, acc);
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(2, kEpiThreads);
+            if (etid == 0) {
+              if (p.op == OP_AR1) {
+                for (int d = 0; d < p.R; ++d) {
+                  tma_store_2d(&p.tma_slot[d], staging, col0, row0);
+                  tma_store_2d(&p.tma_slot[d], staging + BM * 128, col0 + 64, row0);
+                }
+              } else {
+                tma_store_2d(&p.tma_slot[dest], staging, col0, row0);
+                tma_store_2d(&p.tma_slot[dest], staging + BM * 128, col0 + 64, row0);
+              }
+              tma_store_commit();
             }
           }
-          fence_proxy_async_smem();          // generic smem writes -> visible to the bulk copy
-          if (row_ok && col0 < p.N) {
-            if (p.op == OP_AR1) {
-              const int64_t off = static_cast<int64_t>(row) * p.N + col0;
-              for (int d = 0; d < p.R; ++d)
-                bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
+          if (etid == 0) tma_store_wait_all<0>();      // every byte has been written
+        } else {
+        // Each thread owns one accumulator row: it converts 128 columns into its staging
+          // row, then ships the 256 contiguous bytes to every destination with one bulk
+          // copy each (large NVLink writes instead of scattered 16-byte stores).
+          uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
+          for (int half = 0; half < BN / kStageCols; ++half) {
+            const int col0 = t.n_tile * BN + half * kStageCols;
+            tma_store_wait_read<0>();          // my previous copies have read this row
+  #pragma unroll 1
+            for (int c = 0; c < kStageCols / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(taddr + half * kStageCols + c * 32, r);
+              tmem_ld_wait();
+              uint4* d4 = reinterpret_cast<uint4*>(my_stage + c * 64);
+  #pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                d4[v] = o;
+              }
+            }
+            fence_proxy_async_smem();          // generic smem writes -> visible to the bulk copy
+            if (row_ok && col0 < p.N) {
+              if (p.op == OP_AR1) {
+                const int64_t off = static_cast<int64_t>(row) * p.N + col0;
+                for (int d = 0; d < p.R; ++d)
+                  bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
+                                    (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
+                                my_stage, kStageRowBytes);
+              } else if (owner != p.rank) {
+                const int64_t off = (p.op == OP_RS)
+                    ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col0
+                    : static_cast<int64_t>(row) * p.N + col0;
+                bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
                                   (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
                               my_stage, kStageRowBytes);
-            } else if (owner != p.rank) {
-              const int64_t off = (p.op == OP_RS)
-                  ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col0
-                  : static_cast<int64_t>(row) * p.N + col0;
-              bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[owner]) +
-                                (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
-                            my_stage, kStageRowBytes);
+              }
             }
+            tma_store_commit();
           }
-          tma_store_commit();
+          tma_store_wait_all<0>();             // every byte has been written
         }
-        tma_store_wait_all<0>();             // every byte has been written
         fence_acq_rel_sys();
         named_bar_sync(2, kEpiThreads);
         if (p.op == OP_RS) {
@@ -723,10 +804,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
         const bool bcast = kStaging && multi && p.op == OP_AR2;   // reduced tile goes out via staging
-        uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
+        const int r_in_tile = q * 32 + lane;
         for (int c = 0; c < BN / 32; ++c) {
           if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
-          if (bcast && (c & 3) == 0) tma_store_wait_read<0>();
+          const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
+                                                 : t.n_tile * BN + c * 32;
+          if (bcast && (c & 3) == 0) {
+            if (etid == 0) tma_store_wait_read<0>();   // earlier stores have read the staging
+            named_bar_sync(2, kEpiThreads);
+          }
           float acc[32];
           if (multi && p.op == OP_AR1) {
             // all R contributions (own included) are summed from their 16-bit form
@@ -748,66 +834,63 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
           }
-          const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
-                                                 : t.n_tile * BN + c * 32;
-          if (!row_ok || ocol >= p.N) continue;
-
-          if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
-            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                   (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                               acc);
-          } else if (p.op == OP_RS) {
-            if (owner != p.rank) continue;
-            const int lrow = row - owner * p.m_per_rank;
-            // fixed source order keeps the sum deterministic
-            add_rows32_from_sources<kBf16>(
-                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
-                         (static_cast<int64_t>(lrow) * p.N + ocol) * 2,
-                p.slot_stride * 2, p.R, p.rank);
-            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                   (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
-                               acc);
-          } else if (p.op == OP_AR1) {
-            const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-            add_rows32_from_sources<kBf16>(
-                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
-                p.slot_stride * 2, p.R, -1);
-            store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                   (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                               acc);
-          } else {  // OP_AR2, this rank owns the tile
-            const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-            add_rows32_from_sources<kBf16>(
-                acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
-                p.slot_stride * 2, p.R, p.rank);
-            uint4* d4 = reinterpret_cast<uint4*>(my_stage + (c & 3) * 64);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o;
-              o.x = pack2<kBf16>(acc[v * 8 + 0], acc[v * 8 + 1]);
-              o.y = pack2<kBf16>(acc[v * 8 + 2], acc[v * 8 + 3]);
-              o.z = pack2<kBf16>(acc[v * 8 + 4], acc[v * 8 + 5]);
-              o.w = pack2<kBf16>(acc[v * 8 + 6], acc[v * 8 + 7]);
-              d4[v] = o;
-            }
-            if ((c & 3) == 3) {
-              // 128 reduced columns of this row are staged: one bulk copy per destination
-              fence_proxy_async_smem();
-              const int64_t off0 = static_cast<int64_t>(row) * p.N + (ocol - 96);
-              for (int d = 0; d < p.R; ++d) {
-                if (d == p.rank && !p.res_is_c) continue;
-                bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_res[d]) + off0 * 2, my_stage,
-                              kStageRowBytes);
+          const bool active = row_ok && ocol < p.N;
+          if (active) {
+            if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
+              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                     (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                                 acc);
+            } else if (p.op == OP_RS) {
+              if (owner == p.rank) {
+                const int lrow = row - owner * p.m_per_rank;
+                // fixed source order keeps the sum deterministic
+                add_rows32_from_sources<kBf16>(
+                    acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) +
+                             (static_cast<int64_t>(lrow) * p.N + ocol) * 2,
+                    p.slot_stride * 2, p.R, p.rank);
+                store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                       (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
+                                   acc);
               }
+            } else if (p.op == OP_AR1) {
+              const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+              add_rows32_from_sources<kBf16>(
+                  acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
+                  p.slot_stride * 2, p.R, -1);
+              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                     (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                                 acc);
+            } else {  // OP_AR2, this rank owns the tile
+              const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+              add_rows32_from_sources<kBf16>(
+                  acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
+                  p.slot_stride * 2, p.R, p.rank);
               if (!p.res_is_c)
-                bulk_store_1d(reinterpret_cast<uint8_t*>(p.c) +
-                                  (static_cast<int64_t>(row) * ldc + (ocol - 96)) * 2,
-                              my_stage, kStageRowBytes);
-              tma_store_commit();
+                store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
+                                       (static_cast<int64_t>(row) * ldc + ocol) * 2,
+                                   acc);
+            }
+          }
+          if (bcast) {
+            // rows past M stage garbage that the tiled store clips at the tensor edge
+            stage_row32_swizzled<kBf16>(staging, r_in_tile, c & 3, acc);
+            if ((c & 3) == 3) {
+              fence_proxy_async_smem();
+              named_bar_sync(2, kEpiThreads);
+              const int col0 = ocol - 96;
+              if (etid == 0 && col0 < p.N) {
+                // 128 reduced columns are staged: two tiled stores per destination
+                for (int d = 0; d < p.R; ++d) {
+                  if (d == p.rank && !p.res_is_c) continue;
+                  tma_store_2d(&p.tma_res[d], staging, col0, t.m_tile * BM);
+                  tma_store_2d(&p.tma_res[d], staging + BM * 128, col0 + 64, t.m_tile * BM);
+                }
+                tma_store_commit();
+              }
             }
           }
         }
-        if (bcast) tma_store_wait_all<0>();
+        if (bcast && etid == 0) tma_store_wait_all<0>();
       }
 
       // accumulator drained: hand the TMEM buffer back to the MMA warp

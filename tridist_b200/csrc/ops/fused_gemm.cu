@@ -154,6 +154,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.push_parts = d.push_parts > 0 ? d.push_parts : 1;
     p.skip_comm = d.skip_comm;
     p.push_ctas = d.push_ctas;
+    p.push_skip_rounds = d.push_skip_rounds;
     p.ag_counters = reinterpret_cast<uint32_t*>(d.ag_counters);
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
@@ -170,6 +171,16 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
       if (((static_cast<int64_t>(p.chunk_rows) * d.K * 2) / p.push_parts) % 16 != 0)
         throw std::runtime_error("tridist_b200: AG push part size must be a multiple of 16 bytes");
       p.tma_a_ws = make_tmap(p.peer_ws[d.rank], d.M, d.K, d.K, d.bf16);
+    }
+    if (d.R > 1 && (d.op == OP_RS || d.op == OP_AR1 || d.op == OP_AR2)) {
+      // store maps over this rank's slot inside every rank's slot buffer
+      const int64_t slot_rows = (d.op == OP_RS) ? p.m_per_rank : d.M;
+      for (int r = 0; r < d.R; ++r) {
+        uint8_t* base = reinterpret_cast<uint8_t*>(p.peer_slots[r]) +
+                        static_cast<int64_t>(d.rank) * d.slot_stride * 2;
+        p.tma_slot[r] = make_tmap(base, slot_rows, d.N, d.N, d.bf16);
+        if (d.op == OP_AR2) p.tma_res[r] = make_tmap(p.peer_res[r], d.M, d.N, d.N, d.bf16);
+      }
     }
     p.prof = reinterpret_cast<uint64_t*>(d.prof);
     p.env.status = reinterpret_cast<StatusBlock*>(d.status_dev);

@@ -32,7 +32,7 @@ struct GemmPlanDesc {
   int64_t peer_ag_flags[8] = {};
   int64_t ag_counters = 0;
   int64_t arrival_ns = 0;
-  int chunk_rows = 0, n_chunks = 0, push_parts = 0, skip_comm = 0, push_ctas = 0;
+  int chunk_rows = 0, n_chunks = 0, push_parts = 0, skip_comm = 0, push_ctas = 0, push_skip_rounds = 0;
   // reduce-scatter / all-reduce
   int64_t peer_slots[2][8] = {};
   int64_t peer_tile_flags[8] = {};

@@ -139,7 +139,12 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["chunk_rows"] = chunk
             d["n_chunks"] = m_pr // chunk
             d["push_parts"] = _push_parts(chunk)
-            d["push_ctas"] = env_int("TRIDIST_PUSH_CTAS", 0)
+            # A subset of the CTAs drives the push and joins the GEMM one round late: the copy
+            # engine of a pushing SM is busy, which slows that SM's operand loads.
+            units = ((M + 255) // 256) * ((N + (bn // 2 if swiglu else bn) - 1) // (bn // 2 if swiglu else bn))
+            rounds = units / 74.0
+            d["push_ctas"] = env_int("TRIDIST_PUSH_CTAS", 32)
+            d["push_skip_rounds"] = env_int("TRIDIST_PUSH_SKIP", 1 if rounds >= 4 else 0)
         return native().gemm_plan_create(d)
 
     return ctx.plans.get(key, make)

@@ -9,6 +9,9 @@ TRIDIST_WAIT_TIMEOUT_MS   limit of every in-kernel wait (default 4000)
 TRIDIST_MAX_CTAS          cap on the persistent grid of the fused GEMM kernels
 TRIDIST_FORCE_BN          128 or 256: override the output-tile width heuristic
 TRIDIST_CTA_PAIR          0: never run 256-wide tiles on CTA pairs (2-CTA tcgen05 MMA); default 1
+TRIDIST_PUSH_CTAS         CTAs that drive the all-gather push (default 32; 0 = all)
+TRIDIST_PUSH_SKIP         scheduling rounds the pushing CTAs sit out (default 1 on large problems)
+TRIDIST_PROF              1: collect per-CTA stall accounting of the fused GEMM kernels
 TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot"
 TRIDIST_AR_ONE_SHOT_BYTES size threshold (bytes of one rank's partial) below which
                           the one-shot all-reduce is used (default 4 MiB)
