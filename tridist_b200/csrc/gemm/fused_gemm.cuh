@@ -642,9 +642,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const uint32_t use = static_cast<uint32_t>(it >> 1);
       // The four epilogue warps decide together whether to go on: a warp that
       // gave up must never leave the others parked at a named barrier.
-      if (!epi_vote(&s_flags[0],
-                    wait_mbar(&tmem_full_bar[buf], use & 1u, env, SITE_TMEM_FULL, buf)))
-        break;
+      // one lane per warp polls (the other 31 sleep at the warp barrier): the epilogue warps
+      // spend most of the kernel here, and idle polling costs power the tensor cores need
+      bool acc_ready = true;
+      if (lane == 0) acc_ready = wait_mbar(&tmem_full_bar[buf], use & 1u, env, SITE_TMEM_FULL, buf);
+      acc_ready = __shfl_sync(0xFFFFFFFFu, acc_ready ? 1 : 0, 0) != 0;
+      if (!epi_vote(&s_flags[0], acc_ready)) break;
       tc_fence_after_sync();
       const uint64_t t_epi0 = (prof && etid == 0) ? globaltimer_ns() : 0;
 

@@ -97,6 +97,8 @@ def pick_mode(ctx, M: int) -> str:
         return "local"
     if ctx.mode in ("one_shot", "two_shot"):
         return ctx.mode
+    if ctx.num_ranks == 2:
+        return "one_shot"        # same traffic as two-shot at two ranks, one hop less
     limit = env_int("TRIDIST_AR_ONE_SHOT_BYTES", 4 << 20)
     return "one_shot" if M * ctx.N * 2 <= limit else "two_shot"
 
