@@ -59,6 +59,7 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
     for (size_t i = 0; i < v.size() && i < 8; ++i) g.seg_order[i] = v[i];
   }
   g.order_table = get<int64_t>(d, "order_table", 0);
+  g.strided_interleave = get<int>(d, "strided_interleave", 0);
   g.tile_list = get<int64_t>(d, "tile_list", 0);
   g.list_len = get<int>(d, "list_len", 0);
   g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);

@@ -111,6 +111,7 @@ struct alignas(64) GemmParams {
   int32_t unit_m;          // scheduling units along M = ceil(m_tiles / cta_m)
   int32_t seg_m_tiles;     // units per segment (SCHED_SEGMENT)
   int32_t seg_order[kMaxRanks];
+  int32_t strided_interleave;  // SCHED_STRIDED: same unit order on every rank (see tile_at)
   const int32_t* order_table;  // optional device table overriding seg_order (R entries)
   const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
   int32_t list_len;
@@ -191,7 +192,10 @@ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t*
     const int per_owner = (total + p.R - 1) / p.R;
     const int oi = pos / per_owner;
     const int k = pos - oi * per_owner;
-    ulin = order[oi] + k * p.R;
+    // interleaved: every rank walks the units in the same order, so the partials of a unit
+    // reach its owner while the owner computes its own, and the owners' broadcasts spread
+    // over the whole kernel instead of piling up at the end
+    ulin = p.strided_interleave ? pos : order[oi] + k * p.R;
     if (ulin >= total) t.valid = false;
     else raster_grouped(ulin, p.unit_m, p.n_tiles, um, nt);
   } else if (p.sched == SCHED_LIST) {

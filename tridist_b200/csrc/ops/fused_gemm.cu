@@ -139,6 +139,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
       throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
     for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
     p.order_table = reinterpret_cast<const int32_t*>(d.order_table);
+    p.strided_interleave = d.strided_interleave;
     p.tile_list = reinterpret_cast<const int32_t*>(d.tile_list);
     p.list_len = d.list_len;
     p.swiglu_up_row0 = d.swiglu_up_row0;

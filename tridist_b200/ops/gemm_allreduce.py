@@ -126,6 +126,7 @@ def _plan(ctx, a, b, c, mode, parity):
         if op == OP_AR2:
             d["sched"] = SCHED_STRIDED
             d["seg_order"] = rotation_order(rank, R, 1, own_last=True)
+            d["strided_interleave"] = 0 if env_str("TRIDIST_AR2_ORDER", "interleave") == "own_last" else 1
             rhalf = ctx.max_M * ctx.N * 2
             d["peer_res"] = [ctx.res.ptrs(0), ctx.res.ptrs(rhalf)]
             d["peer_res_flags"] = ctx.res_flags.ptrs()
