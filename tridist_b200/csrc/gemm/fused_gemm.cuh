@@ -675,9 +675,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           tile_reduces = (o_lo <= p.rank && p.rank <= o_hi);
           tile_publishes = !(o_lo == p.rank && o_hi == p.rank);
         } else if (p.op == OP_AR2) {
+          // every partial (own included) goes to the owner's slot; the owner's communication
+          // warps reduce and broadcast once all R partials are there, so no epilogue waits
           owner = t.owner_key % p.R;
-          tile_reduces = (owner == p.rank);
-          tile_publishes = !tile_reduces;
+          tile_reduces = false;
+          tile_publishes = true;
         } else if (p.op == OP_AR1) {
           tile_reduces = true;
           tile_publishes = true;
@@ -760,7 +762,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                   bulk_store_1d(reinterpret_cast<uint8_t*>(p.peer_slots[d]) +
                                     (static_cast<int64_t>(p.rank) * p.slot_stride + off) * 2,
                                 my_stage, kStageRowBytes);
-              } else if (owner != p.rank) {
+              } else if (owner != p.rank || p.op == OP_AR2) {
                 const int64_t off = (p.op == OP_RS)
                     ? static_cast<int64_t>(row - owner * p.m_per_rank) * p.N + col0
                     : static_cast<int64_t>(row) * p.N + col0;
@@ -810,7 +812,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool finalizes =
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
-        const bool bcast = kStaging && multi && p.op == OP_AR2;   // reduced tile goes out via staging
+        constexpr bool bcast = false;   // (two-shot tiles are finished by the communication warps)
         const int r_in_tile = q * 32 + lane;
         for (int c = 0; c < BN / 32; ++c) {
           if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
@@ -912,12 +914,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         ++n_tiles_done;
       }
 
-      // ---- two-shot: tell every rank the reduced tile is in its result buffer ------
-      if (multi && p.op == OP_AR2 && tile_reduces) {
-        fence_acq_rel_sys();
-        named_bar_sync(2, kEpiThreads);
-        if (etid < p.R && etid != p.rank) st_release_sys(p.peer_res_flags[etid] + t.linear, p.round);
-      }
       ++it;
     }
     if (prof && etid == 0) {
@@ -996,10 +992,97 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         }
       }
     } else if (p.op == OP_AR2 && p.R > 1) {
-      // Collect the reduced tiles other owners broadcast into this rank's result
-      // buffer; copy them into the caller's tensor unless it aliases the buffer.
       const int tickets = p.unit_m * p.cta_m * p.n_tiles;
+      const int units = p.unit_m * p.n_tiles;
       bool ok = true;
+      // ---- phase A: finish the tiles this rank owns (unit % R == rank), spread over all CTAs --
+      // wait for the R partials of a tile, sum them in fp32 in source order, write the result
+      // into every rank's result buffer with coalesced 16-byte stores, raise the result tickets
+      int owned_seq = 0;
+      for (int unit = p.rank; ok && unit < units; unit += p.R) {
+        for (int subt = 0; ok && subt < p.cta_m; ++subt, ++owned_seq) {
+          if (owned_seq % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          const int lin = unit * p.cta_m + subt;
+          int um, nt;
+          raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
+          const int mt = um * p.cta_m + subt;
+          if (mt * BM >= p.M) continue;
+          if (ctid == 0) s_flags[1] = 1;
+          named_bar_sync(1, kCommThreads);
+          if (ctid < p.R &&
+              !wait_flag_ge(p.peer_tile_flags[p.rank] + ctid * tickets + lin, p.round, env, SITE_AR_TILE,
+                            (ctid << 24) | lin))
+            s_flags[1] = 0;
+          named_bar_sync(1, kCommThreads);     // also orders the slot reads after the acquires
+          ok = s_flags[1] != 0;
+          named_bar_sync(1, kCommThreads);
+          if (!ok) break;
+          const int rows = min(BM, p.M - mt * BM);
+          const int cols = min(BN, p.N - nt * BN);
+          const int vpr = cols >> 3;
+          const int total = rows * vpr;
+          const uint8_t* slots = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]);
+          const int64_t sstride = p.slot_stride * 2;
+          for (int i0 = ctid; i0 < total; i0 += 2 * kCommThreads) {
+            float acc[2][8];
+            int64_t off[2];
+            bool on[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int idx = i0 + u * kCommThreads;
+              on[u] = idx < total;
+              const int r = on[u] ? idx / vpr : 0;
+              const int v = on[u] ? idx - r * vpr : 0;
+              off[u] = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+            }
+            for (int s0 = 0; s0 < p.R; s0 += 4) {
+              uint4 val[2][4];
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  val[u][k] = (on[u] && s0 + k < p.R)
+                                  ? ld_global_cg_v4(slots + (s0 + k) * sstride + off[u] * 2)
+                                  : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint32_t w[4] = {val[u][k].x, val[u][k].y, val[u][k].z, val[u][k].w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack2<kBf16>(w[j]);
+                    acc[u][2 * j] += f.x;
+                    acc[u][2 * j + 1] += f.y;
+                  }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (!on[u]) continue;
+              uint4 o;
+              o.x = pack2<kBf16>(acc[u][0], acc[u][1]);
+              o.y = pack2<kBf16>(acc[u][2], acc[u][3]);
+              o.z = pack2<kBf16>(acc[u][4], acc[u][5]);
+              o.w = pack2<kBf16>(acc[u][6], acc[u][7]);
+              for (int d = 0; d < p.R; ++d) {
+                if (d == p.rank && !p.res_is_c) continue;
+                st_global_v4(reinterpret_cast<uint8_t*>(p.peer_res[d]) + off[u] * 2, o);
+              }
+              if (!p.res_is_c) {
+                const int64_t row = off[u] / p.N, col = off[u] - row * p.N;
+                st_global_v4(reinterpret_cast<uint8_t*>(p.c) + (row * p.ldc + col) * 2, o);
+              }
+            }
+          }
+          fence_acq_rel_sys();
+          named_bar_sync(1, kCommThreads);
+          if (ctid < p.R && ctid != p.rank) st_release_sys(p.peer_res_flags[ctid] + lin, p.round);
+        }
+      }
+      // ---- phase B: collect the tiles the other ranks finished ------------------------------
       for (int lin = blockIdx.x; ok && lin < tickets; lin += gridDim.x) {
         const int unit = lin / p.cta_m;
         if (unit % p.R == p.rank) continue;
