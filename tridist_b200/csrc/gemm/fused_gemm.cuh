@@ -12,13 +12,14 @@
 //                                           rank's own rows are reduced in the epilogue
 //                                           (fp32) from the slots the peers filled
 //   OP_AR1     one-shot all-reduce: every partial tile goes to all peers, each rank reduces
-//   OP_AR2     two-shot all-reduce: tile owner reduces, broadcasts the reduced tile
+//   OP_AR2     two-shot all-reduce: every partial tile goes to the tile's owner; the owner's
+//              communication warps reduce it and broadcast the result to all ranks
 //
 // Roles inside one CTA (320 threads, one CTA per SM):
 //   warp 0      TMA producer (one lane): smem ring of kStages {A 128x64, B BNx64} tiles
 //   warp 1      tcgen05.mma issuer (one lane), owns the TMEM allocation (2 accumulators)
 //   warps 2-5   epilogue: tcgen05.ld -> convert -> global / peer stores (+ in-epilogue reduce)
-//   warps 6-9   communication warps (AG push, AR2 result copy); idle otherwise
+//   warps 6-9   communication warps (AG push; AR2 reduce + broadcast + result collection)
 //
 // Reference behaviour covered (file paths inside the reference project):
 //   triton_dist/kernels/dcu/all_gather_gemm.py:98-230   consumer GEMM gated on flags
@@ -99,9 +100,8 @@ struct alignas(64) GemmParams {
   CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
   CUtensorMap tma_b;       // B [N_rows, K], box 128 rows
   // Store maps (box 128 rows x 64 columns, 128-byte swizzle) over this rank's slot inside
-  // every rank's slot buffer, and over every rank's reduced-result buffer (two-shot).
+  // every rank's slot buffer.
   CUtensorMap tma_slot[kMaxRanks];
-  CUtensorMap tma_res[kMaxRanks];
 
   int32_t M, N, K;         // output is M x N (for EPI_SWIGLU: M x N with B holding 2N rows)
   int32_t m_tiles, n_tiles, k_blocks;
@@ -812,16 +812,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool finalizes =
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
-        constexpr bool bcast = false;   // (two-shot tiles are finished by the communication warps)
-        const int r_in_tile = q * 32 + lane;
         for (int c = 0; c < BN / 32; ++c) {
           if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
           const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
                                                  : t.n_tile * BN + c * 32;
-          if (bcast && (c & 3) == 0) {
-            if (etid == 0) tma_store_wait_read<0>();   // earlier stores have read the staging
-            named_bar_sync(2, kEpiThreads);
-          }
           float acc[32];
           if (multi && p.op == OP_AR1) {
             // all R contributions (own included) are summed from their 16-bit form
@@ -869,37 +863,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
                                      (static_cast<int64_t>(row) * ldc + ocol) * 2,
                                  acc);
-            } else {  // OP_AR2, this rank owns the tile
-              const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
-              add_rows32_from_sources<kBf16>(
-                  acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
-                  p.slot_stride * 2, p.R, p.rank);
-              if (!p.res_is_c)
-                store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                       (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                                   acc);
-            }
-          }
-          if (bcast) {
-            // rows past M stage garbage that the tiled store clips at the tensor edge
-            stage_row32_swizzled<kBf16>(staging, r_in_tile, c & 3, acc);
-            if ((c & 3) == 3) {
-              fence_proxy_async_smem();
-              named_bar_sync(2, kEpiThreads);
-              const int col0 = ocol - 96;
-              if (etid == 0 && col0 < p.N) {
-                // 128 reduced columns are staged: two tiled stores per destination
-                for (int d = 0; d < p.R; ++d) {
-                  if (d == p.rank && !p.res_is_c) continue;
-                  tma_store_2d(&p.tma_res[d], staging, col0, t.m_tile * BM);
-                  tma_store_2d(&p.tma_res[d], staging + BM * 128, col0 + 64, t.m_tile * BM);
-                }
-                tma_store_commit();
-              }
             }
           }
         }
-        if (bcast && etid == 0) tma_store_wait_all<0>();
       }
 
       // accumulator drained: hand the TMEM buffer back to the MMA warp

@@ -180,7 +180,6 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
         uint8_t* base = reinterpret_cast<uint8_t*>(p.peer_slots[r]) +
                         static_cast<int64_t>(d.rank) * d.slot_stride * 2;
         p.tma_slot[r] = make_tmap(base, slot_rows, d.N, d.N, d.bf16);
-        if (d.op == OP_AR2) p.tma_res[r] = make_tmap(p.peer_res[r], d.M, d.N, d.N, d.bf16);
       }
     }
     p.prof = reinterpret_cast<uint64_t*>(d.prof);
