@@ -285,3 +285,123 @@ def test_spot_verify_flags_bad_tile():
     C.spot_verify(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, K, K, N, False, 4, 2e-2, bad.data_ptr(), 256)
     torch.cuda.synchronize()
     assert bad.tolist() == [0, 0, 0, 1]
+
+
+def test_skew_layer_order_table_and_observer_emulated():
+    """Table-driven source order (device int32 table) gives the same C as the default order, and the
+    consumer's arrival stamps come back for every remote source."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    from tridist_b200.parallel.predictor import infer_straggler
+    from tridist_b200.utils.testing import ag_inputs
+    R = 4
+    w = _emu(R)
+    dt = torch.float16
+    m_pr, K, n_pr = 128, 256, 256
+    ctxs = [create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, r, R, M_PER_CHUNK=128, world=w) for r in range(R)]
+    ins = [ag_inputs(r, R, m_pr, K, n_pr, 0, dt, 0.05) for r in range(R)]
+    a_list = [ins[r][0][r].cuda() for r in range(R)]
+    b_list = [ins[r][1].cuda() for r in range(R)]
+    c_ref = [torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda") for _ in range(R)]
+    ag_gemm_emulated(ctxs, a_list, b_list, c_ref)
+    torch.cuda.synchronize()
+    for r, ctx in enumerate(ctxs):                         # own first, "straggler" (r+1) last
+        order = [r] + [x for x in range(R) if x not in (r, (r + 1) % R)] + [(r + 1) % R]
+        ctx.emu_order_table = torch.tensor(order, dtype=torch.int32, device="cuda")
+        ctx.observe = True
+        ctx.arrival_ns.fill_(torch.iinfo(torch.int64).max)
+    c_tab = [torch.empty_like(c) for c in c_ref]
+    ag_gemm_emulated(ctxs, a_list, b_list, c_tab)
+    torch.cuda.synchronize()
+    w.check()
+    for r in range(R):
+        assert torch.equal(c_tab[r], c_ref[r])
+        stamps = ctxs[r].arrival_ns.cpu().tolist()
+        remote = [s for s in range(R) if s != r]
+        assert all(0 < stamps[s] < torch.iinfo(torch.int64).max for s in remote)
+        assert infer_straggler(stamps, r) in remote
+
+
+def test_verify_and_repair_single_rank(monkeypatch):
+    from tridist_b200.ops import create_i1_context, i1_ag_tr_op, i1_observer_read, i1_table_peek, i1_table_write
+    from tridist_b200.ops.ag_tr_pred import _verify_and_repair
+    w = _world1()
+    dt = torch.bfloat16
+    M, K, N = 512, 256, 512
+    torch.manual_seed(11)
+    a = (torch.randn(M, K, device="cuda") * 0.1).to(dt)
+    b = (torch.randn(N, K, device="cuda") * 0.1).to(dt)
+    c = torch.empty(M, N, dtype=dt, device="cuda")
+    ictx = create_i1_context(M, K, dt, dt, 0, 1, world=w)
+    i1_table_write(ictx, 7, 0, 1, 0, 1)
+    assert i1_table_peek(ictx)[:4] == [7, 0, 1, 1]
+    i1_ag_tr_op(a, b, c, ictx)
+    torch.cuda.synchronize()
+    good = c.clone()
+    assert (good.float() - a.float() @ b.float().t()).abs().max().item() < TOL
+    assert _verify_and_repair(a, b, c, ictx) == 0         # nothing to repair
+    c[128:256, 256:] = 0                                  # damage one tile of the result
+    fixed = _verify_and_repair(a, b, c, ictx)
+    torch.cuda.synchronize()
+    assert fixed >= 1 and torch.equal(c, good)
+    assert i1_observer_read(ictx)[1] == 0
+
+
+def test_order_driven_ar_carrier_and_gates_single_rank():
+    from tridist_b200.ops import (create_gemm_ar_rd_context, gemm_ar_pred_op, make_gate_flag, task_events)
+    w = _world1()
+    dt = torch.float16
+    M, N, K = 256, 256, 128
+    torch.manual_seed(12)
+    a = (torch.randn(M, K, device="cuda") * 0.1).to(dt)
+    b = (torch.randn(N, K, device="cuda") * 0.1).to(dt)
+    ctx = create_gemm_ar_rd_context(M, N, dt, dt, 0, 1, world=w)
+    ctx.chunk_rows = 64
+    gate = make_gate_flag()
+    gate[0] = 5                                           # already released
+    c = torch.zeros(M, N, dtype=dt, device="cuda")
+    gemm_ar_pred_op(a, b, c, ctx, order=[3, 1, 0, 2], gates=[(1, gate.data_ptr(), 5)])
+    torch.cuda.synchronize()
+    w.check()
+    assert (c.float() - a.float() @ b.float().t()).abs().max().item() < TOL
+    ev = task_events(ctx)
+    assert len(ev) == 4 and all(e is not None and e[0].elapsed_time(e[1]) >= 0 for e in ev)
+
+
+def test_symm_host_one_sided_calls():
+    from tridist_b200.parallel.symm_host import SymmHost
+    w = _world1()
+    h = SymmHost(w)
+    assert h.my_pe() == 0 and h.n_pes() == 1
+    buf = h.malloc(4096)
+    src = torch.arange(256, dtype=torch.int32, device="cuda")
+    h.putmem(buf, 1024, src, pe=0)
+    dst = torch.zeros_like(src)
+    h.getmem(dst, buf, 1024, pe=0)
+    h.quiet()
+    assert torch.equal(src, dst) and h.ptr(buf, 0, 16) == buf.local_ptr + 16
+    h.set_signal(buf, 3, 9, pe=0)
+    h.wait_signal(buf, 3, 9, timeout_ms=200)
+    h.barrier_all()
+    torch.cuda.synchronize()
+    w.check()
+    h.free(buf)
+
+
+@pytest.mark.parametrize("mode", ["ag_rs", "gemm_ar"])
+def test_tp_mlp_single_rank(mode):
+    from tridist_b200.models.tp_mlp import TPMLP, TPMLPConfig, reference_forward
+    w = _world1()
+    dt = torch.bfloat16
+    M, K, I = 256, 256, 384
+    torch.manual_seed(13)
+    x = torch.randn(M, K, device="cuda").to(dt)
+    w_gu = (torch.randn(2 * I, K, device="cuda") * 0.05).to(dt)
+    w_d = (torch.randn(K, I, device="cuda") * 0.05).to(dt)
+    ref = reference_forward(x, [w_gu], [w_d])
+    for fuse in ([True, False] if mode == "ag_rs" else [False]):
+        layer = TPMLP(TPMLPConfig(hidden=K, intermediate=I, max_tokens=M, dtype=dt, mode=mode, fuse_swiglu=fuse),
+                      0, 1, w_gu, w_d, world=w)
+        y = layer(x)
+        torch.cuda.synchronize()
+        w.check()
+        assert (y.float() - ref).abs().max().item() < 3e-2

@@ -117,8 +117,10 @@ def _plan(ctx, a, b, c, swiglu=False):
     N = n_rows // 2 if swiglu else n_rows
     bn = choose_bn(M, N, swiglu)
     order = ctx.order_override or rotation_order(rank, R, 1, own_last=False)
+    # emulated launches cannot take a per-call table: a device order table is baked into the plan
+    baked_table = getattr(ctx, "emu_order_table", None)
     key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, c.stride(0), a.dtype, swiglu, bn,
-           tuple(order))
+           tuple(order), baked_table.data_ptr() if baked_table is not None else 0, ctx.observe)
 
     def make():
         d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, OP_AG)
@@ -126,6 +128,8 @@ def _plan(ctx, a, b, c, swiglu=False):
         d["m_per_rank"] = m_pr
         d["sched"] = SCHED_SEGMENT if (m_pr % BM == 0) else SCHED_NATURAL
         d["seg_order"] = order
+        if baked_table is not None:
+            d["order_table"] = baked_table.data_ptr()
         if swiglu:
             d["epi"] = EPI_SWIGLU
             d["swiglu_up_row0"] = N
