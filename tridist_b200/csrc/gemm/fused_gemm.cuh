@@ -349,7 +349,7 @@ __device__ __forceinline__ bool epi_vote(volatile int32_t* flag, bool my_ok) {
   return !dead;
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // ----------------------------------------------------------------------------
 // The kernel

@@ -28,14 +28,14 @@ __device__ __forceinline__ uint32_t swiglu2(uint32_t g, uint32_t u) {
   if constexpr (kBf16) {
     const float2 gf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&g));
     const float2 uf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
-    __nv_bfloat162 r = __floats2bfloat162_rn(gf.x / (1.f + __expf(-gf.x)) * uf.x,
-                                             gf.y / (1.f + __expf(-gf.y)) * uf.y);
+    __nv_bfloat162 r = __floats2bfloat162_rn(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x,
+                                             __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
     return *reinterpret_cast<uint32_t*>(&r);
   } else {
     const float2 gf = __half22float2(*reinterpret_cast<__half2*>(&g));
     const float2 uf = __half22float2(*reinterpret_cast<__half2*>(&u));
-    __half2 r = __floats2half2_rn(gf.x / (1.f + __expf(-gf.x)) * uf.x,
-                                  gf.y / (1.f + __expf(-gf.y)) * uf.y);
+    __half2 r = __floats2half2_rn(__fdividef(gf.x, 1.f + __expf(-gf.x)) * uf.x,
+                                  __fdividef(gf.y, 1.f + __expf(-gf.y)) * uf.y);
     return *reinterpret_cast<uint32_t*>(&r);
   }
 }
@@ -46,19 +46,32 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint8_t* __restrict__
                                                      int64_t inter, int64_t ldh) {
   const int64_t vec_per_row = inter >> 3;
   const int64_t total = rows * vec_per_row;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / vec_per_row;
-    const int64_t v = i - r * vec_per_row;
-    const uint8_t* row = h + r * ldh * 2;
-    const uint4 g = ld_global_nc_v4(row + v * 16);
-    const uint4 u = ld_global_nc_v4(row + inter * 2 + v * 16);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // two independent 16-byte gate/up pairs per iteration keep four loads in flight per thread
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += 2 * stride) {
+    const int64_t i2 = i + stride;
+    const bool two = i2 < total;
+    const int64_t r0 = i / vec_per_row, v0 = i - r0 * vec_per_row;
+    const int64_t r1 = two ? i2 / vec_per_row : r0, v1 = two ? i2 - r1 * vec_per_row : v0;
+    const uint8_t* row0 = h + r0 * ldh * 2;
+    const uint8_t* row1 = h + r1 * ldh * 2;
+    const uint4 g0 = ld_global_nc_v4(row0 + v0 * 16);
+    const uint4 u0 = ld_global_nc_v4(row0 + inter * 2 + v0 * 16);
+    const uint4 g1 = ld_global_nc_v4(row1 + v1 * 16);
+    const uint4 u1 = ld_global_nc_v4(row1 + inter * 2 + v1 * 16);
     uint4 o;
-    o.x = swiglu2<kBf16>(g.x, u.x);
-    o.y = swiglu2<kBf16>(g.y, u.y);
-    o.z = swiglu2<kBf16>(g.z, u.z);
-    o.w = swiglu2<kBf16>(g.w, u.w);
-    st_global_v4(out + (r * inter + v * 8) * 2, o);
+    o.x = swiglu2<kBf16>(g0.x, u0.x);
+    o.y = swiglu2<kBf16>(g0.y, u0.y);
+    o.z = swiglu2<kBf16>(g0.z, u0.z);
+    o.w = swiglu2<kBf16>(g0.w, u0.w);
+    st_global_v4(out + (r0 * inter + v0 * 8) * 2, o);
+    if (two) {
+      o.x = swiglu2<kBf16>(g1.x, u1.x);
+      o.y = swiglu2<kBf16>(g1.y, u1.y);
+      o.z = swiglu2<kBf16>(g1.z, u1.z);
+      o.w = swiglu2<kBf16>(g1.w, u1.w);
+      st_global_v4(out + (r1 * inter + v1 * 8) * 2, o);
+    }
   }
 }
 
