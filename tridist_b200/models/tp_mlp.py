@@ -106,6 +106,16 @@ class TPMLP:
 
     __call__ = forward
 
+    def close(self) -> None:
+        """Collective: release the symmetric buffers of the layer's operator contexts."""
+        from ..ops import finalize_ag_gemm_context, finalize_gemm_ar_context, finalize_gemm_rs_context
+        if self.cfg.mode == "ag_rs":
+            finalize_ag_gemm_context(self.ag)
+            finalize_gemm_rs_context(self.rs)
+        else:
+            finalize_gemm_ar_context(self.ar1)
+            finalize_gemm_ar_context(self.ar2)
+
 
 def reference_forward(x_full: torch.Tensor, w_gu_shards, w_down_shards) -> torch.Tensor:
     """fp32 reference of the ag_rs layout: shards are per-rank [2I/R, K] and [K, I/R]."""
