@@ -191,7 +191,7 @@ def main() -> None:
             "impl": "ours",
             "config": {
                 "model": "GPT-3-175B MLP (AG+GEMM, GEMM+RS) + GEMM+AR K=28672 N=8192 M in {128,1024,4096} + "
-                         "MoE a2a E64 H4096 T4096/rank topk8 (uniform, Zipf 1.2) + Llama-3-70B TP-MLP fwd",
+                         "MoE a2a E64 H4096 32768 tokens total (4096/rank at 8 GPUs) topk8 (uniform, Zipf 1.2) + Llama-3-70B TP-MLP fwd",
                 "global_batch": 8192, "seq_len": 1, "parallelism": f"tp{world}" + ("+ep%d" % world),
                 "step": "one run of each workload: " + ",".join(names),
                 "l2": "256 MB buffer overwritten before every operator (inside the step time)",

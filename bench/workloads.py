@@ -256,8 +256,10 @@ def build_all(rank: int, R: int, only: Optional[List[str]] = None) -> List[Workl
         "gemm_ar_m128": lambda: GemmAR(rank, R, 128),
         "gemm_ar_m1024": lambda: GemmAR(rank, R, 1024),
         "gemm_ar_m4096": lambda: GemmAR(rank, R, 4096),
-        "moe_a2a_uniform": lambda: MoE(rank, R, 0.0),
-        "moe_a2a_zipf": lambda: MoE(rank, R, 1.2),
+        # 32768 tokens in total (4096 per rank at 8 GPUs, the named configuration): the step's
+        # total work stays fixed as the GPU count changes
+        "moe_a2a_uniform": lambda: MoE(rank, R, 0.0, T=32768 // R),
+        "moe_a2a_zipf": lambda: MoE(rank, R, 1.2, T=32768 // R),
         "tp_mlp": lambda: TPMLPLayer(rank, R),
     }
     names = only or list(makers)
