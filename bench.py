@@ -21,6 +21,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import time
 import statistics
 import sys
 
@@ -101,26 +102,30 @@ def main() -> None:
             if events is not None:
                 events[i][1].record()
 
+    # the clock sampler runs from before the warm-up (nvidia-smi needs ~0.1 s to deliver its first
+    # line); only the samples that arrive inside the timed region are reported when there are any
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step()
     sync_all()
 
     # ---- timed region: exactly K steps -------------------------------------------------
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in wls]
            for _ in range(args.steps)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = C.launch_count()
     sync_all()
+    w0 = time.monotonic()
     t0.record()
     for k in range(args.steps):
         step(evs[k])
     t1.record()
     sync_all()
+    w1 = time.monotonic()
     launches = C.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else {}
+    clocks = sampler.stop((w0, w1)) if rank == 0 else {}
     rt.check()
     total_ms = max_over_ranks([t0.elapsed_time(t1)])[0]
     ms_per_step = total_ms / args.steps
@@ -204,6 +209,7 @@ def main() -> None:
         print(json.dumps(out))
     sync_all()
     if world > 1:
+        rt.release_multicast()      # no rank leaves while bound to a multicast object
         dist.destroy_process_group()
 
 

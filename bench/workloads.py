@@ -154,7 +154,7 @@ class GemmAR(Workload):
 
     def roof(self):
         from tridist_b200.ops.gemm_allreduce import pick_mode
-        two = pick_mode(self.ctx, self.M) == "two_shot"
+        two = pick_mode(self.ctx, self.M) in ("two_shot", "nvls")
         return roofline.gemm_ar_roof(self.M, self.N, self.k_loc, self.R, two_shot=two)
 
     def check(self):

@@ -77,3 +77,64 @@ def _all_ops(rank, R):
 def test_all_ops_two_gpus():
     from tridist_b200.utils.testing import spawn
     spawn(_all_ops, 2, backend="nccl", timeout=600)
+
+
+def _nvls_all_reduce(rank, R):
+    """GEMM + all-reduce with the sum and the replication done by the NVSwitch (multimem).
+    Errors are collected and raised only after the multicast buffer has been released by all
+    ranks together: no rank leaves while its memory is still bound to the multicast object."""
+    import torch.distributed as dist
+    from tridist_b200.ops import create_gemm_ar_intra_node_context, gemm_ar_intra_node, gemm_ar_intra_node_op
+    from tridist_b200.ops.gemm_allreduce import finalize_gemm_ar_context, pick_mode
+    from tridist_b200.parallel.runtime import init_runtime
+    from tridist_b200.utils.testing import ks_inputs
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    w = init_runtime(rank, R)
+    dt = torch.bfloat16
+    max_M, N, kl = 1024, 768, 512
+    ar = create_gemm_ar_intra_node_context(max_M, N, dt, dt, rank, R, nvls=True)
+    if ar.mc is None:
+        if rank == 0:
+            print("NVLS unavailable:", getattr(w, "multicast_unavailable", "?"), flush=True)
+        finalize_gemm_ar_context(ar)
+        return
+    problems = []
+    try:
+        ar.mode = "nvls"
+        assert pick_mode(ar, max_M) == "nvls"
+        for it, M in enumerate([1024, 1024, 512, 128, 1024, 256]):
+            a_all, b_all = ks_inputs(R, M, N, kl, it, dt)
+            ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
+            a, b = a_all[rank].cuda(), b_all[rank].cuda()
+            if it % 2 == 0:
+                c = torch.empty(M, N, dtype=dt, device="cuda")
+                gemm_ar_intra_node_op(a, b, c, ar)
+            else:
+                c = gemm_ar_intra_node(a, b, ar)          # view of the symmetric result plane
+            torch.cuda.synchronize()
+            w.check()
+            err = (c.float() - ref).abs().max().item()
+            if not err < 4e-2:
+                problems.append(f"round {it} M={M}: max error {err}")
+            # reduced once by the owner, replicated by the switch: identical bits everywhere
+            digest = c.view(torch.int16).to(torch.int64).sum().reshape(1)
+            lo, hi = digest.clone(), digest.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            if lo.item() != hi.item():
+                problems.append(f"round {it}: ranks hold different results")
+    except Exception as exc:                              # reported after the collective release
+        problems.append(f"{type(exc).__name__}: {exc}")
+    finally:
+        try:
+            finalize_gemm_ar_context(ar)
+        except Exception as exc:
+            problems.append(f"release failed: {exc}")
+    if rank == 0:
+        print("NVLS all-reduce:", "ok" if not problems else problems, flush=True)
+    assert not problems, problems
+
+
+def test_nvls_all_reduce_two_gpus():
+    from tridist_b200.utils.testing import spawn
+    spawn(_nvls_all_reduce, 2, backend="nccl", timeout=300)

@@ -81,10 +81,20 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   fill_ptrs2(d, "peer_res", g.peer_res);
   fill_ptrs(d, "peer_res_flags", g.peer_res_flags, 8);
   g.res_is_c = get<int>(d, "res_is_c", 0);
+  g.nvls = get<int>(d, "nvls", 0);
+  if (d.contains("mc_part")) {
+    auto v = d["mc_part"].cast<std::vector<int64_t>>();
+    for (size_t i = 0; i < v.size() && i < 2; ++i) g.mc_part[i] = v[i];
+  }
+  if (d.contains("mc_res")) {
+    auto v = d["mc_res"].cast<std::vector<int64_t>>();
+    for (size_t i = 0; i < v.size() && i < 2; ++i) g.mc_res[i] = v[i];
+  }
   g.prof = get<int64_t>(d, "prof", 0);
   g.status_dev = get<int64_t>(d, "status_dev", 0);
   g.abort_word = get<int64_t>(d, "abort_word", 0);
   g.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
+  g.poll_ns = get<uint32_t>(d, "poll_ns", 0u);
   return gemm_plan_create(g);
 }
 
@@ -195,6 +205,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("fill_u32", [](int64_t p, int64_t n, uint32_t v) {
     fill_u32_launch(reinterpret_cast<uint32_t*>(p), n, v, cur_stream());
+  });
+  m.def("multimem_probe", [](int64_t mc_in, int64_t mc_out, int64_t local_out, int64_t begin, int64_t end,
+                             int blocks, int threads, int unroll, bool weak, bool local_store) {
+    multimem_probe_launch(mc_in, mc_out, local_out, begin, end, blocks, threads, unroll, weak, local_store,
+                          cur_stream());
   });
   m.def("spot_verify", [](int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           bool bf16, int spots, float tol, int64_t bad_tiles, int bn) {

@@ -148,6 +148,34 @@ __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
 }
 
 // ----------------------------------------------------------------------------
+// NVSwitch multicast (multimem) on addresses of a multicast mapping
+// ----------------------------------------------------------------------------
+// Sum of the eight 16-bit values held at the same offset in every GPU bound to the multicast
+// object: the switch reads all copies and adds them (fp32 accumulation), one 16-byte reply.
+template <bool kBf16>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_v4(const void* mc) {
+  uint4 v;
+  if constexpr (kBf16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+  }
+  return v;
+}
+// One 16-byte store that the switch replicates into every bound GPU's copy.
+__device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// ----------------------------------------------------------------------------
 // TMA
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

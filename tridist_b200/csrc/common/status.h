@@ -46,6 +46,7 @@ struct WaitEnv {
   uint32_t* abort_word;     // device memory, one word per context; non-zero = give up
   uint64_t timeout_ns;      // limit for a single wait
   uint32_t rank;
+  uint32_t poll_ns;         // pause between two polls of a flag (0 = poll back to back)
 };
 
 }  // namespace tdb

@@ -31,26 +31,32 @@ __device__ __forceinline__ bool aborted(const WaitEnv& env) {
   return env.abort_word != nullptr && *reinterpret_cast<volatile uint32_t*>(env.abort_word) != 0u;
 }
 
-// Spin until *flag >= ticket (monotonic tickets; wrap-safe signed difference).
-// The successful read is an acquire at system scope.
+// Spin until *flag >= ticket (monotonic tickets; wrap-safe signed difference). The polls are
+// relaxed loads (an acquire per poll would run its cache maintenance hundreds of times while
+// the tensor pipeline of the same SM is streaming); one acquire load follows the poll that
+// saw the ticket, which is what orders the caller's reads of the published data.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t ticket,
                                              const WaitEnv& env, uint32_t site, uint32_t aux) {
-  uint32_t v = ld_acquire_sys(flag);
-  if (static_cast<int32_t>(v - ticket) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t it = 0;
-  while (true) {
-    v = ld_acquire_sys(flag);
-    if (static_cast<int32_t>(v - ticket) >= 0) return true;
-    if ((++it & 63u) == 0u) {
-      if (aborted(env)) return false;
-      if (globaltimer_ns() - t0 > env.timeout_ns) {
-        report_failure(env, ST_TIMEOUT_FLAG, site, ticket, v, aux);
-        return false;
+  uint32_t v = ld_relaxed_sys(flag);
+  if (static_cast<int32_t>(v - ticket) < 0) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (true) {
+      if (env.poll_ns) __nanosleep(env.poll_ns);
+      v = ld_relaxed_sys(flag);
+      if (static_cast<int32_t>(v - ticket) >= 0) break;
+      if ((++it & 63u) == 0u) {
+        if (aborted(env)) return false;
+        if (globaltimer_ns() - t0 > env.timeout_ns) {
+          report_failure(env, ST_TIMEOUT_FLAG, site, ticket, v, aux);
+          return false;
+        }
+        __nanosleep(64);
       }
-      __nanosleep(64);
     }
   }
+  v = ld_acquire_sys(flag);          // tickets only grow: still >= ticket
+  return static_cast<int32_t>(v - ticket) >= 0;
 }
 
 // Wait for an mbarrier phase with the same limit.

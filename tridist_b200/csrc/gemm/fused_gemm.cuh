@@ -92,7 +92,25 @@ enum ProfSlot : int {
   PROF_EPI_TILES = 7,        // epilogue: tiles processed (count)
   PROF_PUSH_TOTAL = 8,       // communication warps: whole push / collect loop
   PROF_KERNEL = 9,           // CTA lifetime
-  kProfSlots = 16,
+  PROF_AR_A_WAIT = 10,       // two-shot all-reduce, owner side: waiting for the R partials of owned tiles
+  PROF_AR_A_WORK = 11,       // owner side: reduce + broadcast + fence + result tickets
+  PROF_AR_B_WAIT = 12,       // collector side: waiting for result tickets
+  PROF_AR_B_COPY = 13,       // collector side: result buffer -> c
+  PROF_EPI_DONE_AT = 14,     // kernel start -> last tile left the epilogue
+  PROF_AR_A_DONE_AT = 15,    // kernel start -> last owned tile broadcast
+  // time stamps (ns since this CTA started) of the LAST tile each role handled
+  PROF_TL_ACC_READY = 16,    // epilogue: accumulator ready
+  PROF_TL_STAGED = 17,       // epilogue: partial converted, all bulk stores issued
+  PROF_TL_STORED = 18,       // epilogue: bulk stores complete
+  PROF_TL_FLAGGED = 19,      // epilogue: tile ticket(s) released
+  PROF_TL_OWN_SEEN = 20,     // owner: all R partial tickets seen
+  PROF_TL_OWN_LOADED = 21,   // owner: reduce / broadcast loop done
+  PROF_TL_OWN_FENCED = 22,   // owner: system fence + barrier passed
+  PROF_TL_OWN_FLAGGED = 23,  // owner: result tickets released
+  PROF_TL_COL_SEEN = 24,     // collector: last result ticket seen
+  PROF_TL_COMM_START = 25,   // communication warps: entry
+  PROF_TL_OWN_IT0 = 26,      // owner: first batch of the reduce loop stored (cold-start cost)
+  kProfSlots = 32,
 };
 
 struct alignas(64) GemmParams {
@@ -142,6 +160,12 @@ struct alignas(64) GemmParams {
   void* peer_res[kMaxRanks];       // OP_AR2: reduced-result buffer [M][N] on every rank
   uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [tiles] tickets
   int32_t res_is_c;                // OP_AR2: caller's c aliases peer_res[rank]; skip the copy
+  // OP_AR2 through the switch: partials stay in this rank's own buffer (peer_slots[*] all name
+  // it, slot_stride = 0); the owner of a tile sums the R copies with multimem.ld_reduce on
+  // mc_part and writes the result into every rank's result buffer with multimem.st on mc_res.
+  int32_t nvls;
+  void* mc_part;                   // multicast address of the partial buffer [M][N] (this parity)
+  void* mc_res;                    // multicast address of the result buffer [M][N] (this parity)
 
   // Optional stall accounting: [gridDim.x][kProfSlots] nanosecond sums written at kernel end
   // (see ProfSlot); nullptr = off, no timer is read.
@@ -654,6 +678,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       if (!epi_vote(&s_flags[0], acc_ready)) break;
       tc_fence_after_sync();
       const uint64_t t_epi0 = (prof && etid == 0) ? globaltimer_ns() : 0;
+      if (prof && etid == 0) prof[PROF_TL_ACC_READY] = t_epi0 - t_kernel0;
 
       const int row = t.m_tile * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -729,7 +754,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               tma_store_commit();
             }
           }
+          if (prof && etid == 0) prof[PROF_TL_STAGED] = globaltimer_ns() - t_kernel0;
           if (etid == 0) tma_store_wait_all<0>();      // every byte has been written
+          if (prof && etid == 0) prof[PROF_TL_STORED] = globaltimer_ns() - t_kernel0;
         } else {
         // Each thread owns one accumulator row: it converts 128 columns into its staging
           // row, then ships the 256 contiguous bytes to every destination with one bulk
@@ -775,7 +802,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           }
           tma_store_wait_all<0>();             // every byte has been written
         }
-        fence_acq_rel_sys();
+        // Every thread has seen its own bulk stores complete. The barrier orders them before the
+        // ticket stores below, whose release (one system fence per storing warp, cumulative over
+        // what the barrier ordered) publishes them: a fence in all 128 threads here cost 10-20 us.
         named_bar_sync(2, kEpiThreads);
         if (p.op == OP_RS) {
           const int o = o_lo + etid;
@@ -787,6 +816,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         } else if (etid == 0) {
           st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + t.linear, p.round);
         }
+        if (prof && etid == 0) prof[PROF_TL_FLAGGED] = globaltimer_ns() - t_kernel0;
       }
 
       const uint64_t t_pub1 = (prof && etid == 0) ? globaltimer_ns() : 0;
@@ -887,6 +917,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       prof[PROF_EPI_PUBLISH] = acc_pub;
       prof[PROF_EPI_TICKET_WAIT] = acc_tick;
       prof[PROF_EPI_TILES] = n_tiles_done;
+      prof[PROF_EPI_DONE_AT] = globaltimer_ns() - t_kernel0;
     }
   }
   // ==========================================================================
@@ -965,6 +996,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // wait for the R partials of a tile, sum them in fp32 in source order, write the result
       // into every rank's result buffer with coalesced 16-byte stores, raise the result tickets
       int owned_seq = 0;
+      const bool cprof = prof && ctid == 0;
+      if (cprof) prof[PROF_TL_COMM_START] = globaltimer_ns() - t_kernel0;
+      uint64_t acc_aw = 0, acc_ak = 0, acc_bw = 0, acc_bc = 0;
       for (int unit = p.rank; ok && unit < units; unit += p.R) {
         for (int subt = 0; ok && subt < p.cta_m; ++subt, ++owned_seq) {
           if (owned_seq % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
@@ -973,6 +1007,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
           const int mt = um * p.cta_m + subt;
           if (mt * BM >= p.M) continue;
+          const uint64_t ta0 = cprof ? globaltimer_ns() : 0;
           if (ctid == 0) s_flags[1] = 1;
           named_bar_sync(1, kCommThreads);
           if (ctid < p.R &&
@@ -983,10 +1018,44 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           ok = s_flags[1] != 0;
           named_bar_sync(1, kCommThreads);
           if (!ok) break;
+          const uint64_t ta1 = cprof ? globaltimer_ns() : 0;
+          if (cprof) prof[PROF_TL_OWN_SEEN] = ta1 - t_kernel0;
           const int rows = min(BM, p.M - mt * BM);
           const int cols = min(BN, p.N - nt * BN);
           const int vpr = cols >> 3;
           const int total = rows * vpr;
+          if (p.nvls) {
+            // the switch adds the R copies of a 16-byte piece on the way here and replicates
+            // the result on the way back: one load and one store per piece, whatever R is
+            constexpr int kU = 16;
+            uint8_t* mc_in = reinterpret_cast<uint8_t*>(p.mc_part);
+            uint8_t* mc_out = reinterpret_cast<uint8_t*>(p.mc_res);
+            for (int i0 = ctid; i0 < total; i0 += kU * kCommThreads) {
+              uint4 val[kU];
+              // all loads of the batch are issued before the first store needs its value; pieces
+              // past the end of the tile re-read its last piece (no branch between the loads)
+#pragma unroll
+              for (int u = 0; u < kU; ++u) {
+                const int idx = min(i0 + u * kCommThreads, total - 1);
+                const int r = idx / vpr;
+                const int v = idx - r * vpr;
+                const int64_t off = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
+                val[u] = multimem_ld_reduce_add_v4<kBf16>(mc_in + off * 2);
+              }
+#pragma unroll
+              for (int u = 0; u < kU; ++u) {
+                const int idx = i0 + u * kCommThreads;
+                if (idx >= total) break;
+                const int r = idx / vpr;
+                const int v = idx - r * vpr;
+                const int64_t row = mt * BM + r, col = nt * BN + v * 8;
+                multimem_st_v4(mc_out + (row * p.N + col) * 2, val[u]);
+                if (!p.res_is_c)
+                  st_global_v4(reinterpret_cast<uint8_t*>(p.c) + (row * p.ldc + col) * 2, val[u]);
+              }
+              if (cprof && i0 == ctid) prof[PROF_TL_OWN_IT0] = globaltimer_ns() - t_kernel0;
+            }
+          } else {
           const uint8_t* slots = reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]);
           const int64_t sstride = p.slot_stride * 2;
           for (int i0 = ctid; i0 < total; i0 += 2 * kCommThreads) {
@@ -1042,11 +1111,25 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                 st_global_v4(reinterpret_cast<uint8_t*>(p.c) + (row * p.ldc + col) * 2, o);
               }
             }
+            if (cprof && i0 == ctid) prof[PROF_TL_OWN_IT0] = globaltimer_ns() - t_kernel0;
           }
-          fence_acq_rel_sys();
+          }
+          if (cprof) prof[PROF_TL_OWN_LOADED] = globaltimer_ns() - t_kernel0;
+          // the releases below (one warp) are cumulative over the stores this barrier orders
           named_bar_sync(1, kCommThreads);
+          if (cprof) prof[PROF_TL_OWN_FENCED] = globaltimer_ns() - t_kernel0;
           if (ctid < p.R && ctid != p.rank) st_release_sys(p.peer_res_flags[ctid] + lin, p.round);
+          if (cprof) {
+            prof[PROF_TL_OWN_FLAGGED] = globaltimer_ns() - t_kernel0;
+            acc_aw += ta1 - ta0;
+            acc_ak += globaltimer_ns() - ta1;
+          }
         }
+      }
+      if (cprof) {
+        prof[PROF_AR_A_WAIT] = acc_aw;
+        prof[PROF_AR_A_WORK] = acc_ak;
+        prof[PROF_AR_A_DONE_AT] = globaltimer_ns() - t_kernel0;
       }
       // ---- phase B: collect the tiles the other ranks finished ------------------------------
       for (int lin = blockIdx.x; ok && lin < tickets; lin += gridDim.x) {
@@ -1056,6 +1139,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
         const int mt = um * p.cta_m + (lin - unit * p.cta_m);
         if (mt * BM >= p.M) continue;         // nothing is ever published for an empty row block
+        const uint64_t tb0 = cprof ? globaltimer_ns() : 0;
         if (ctid == 0)
           ok = wait_flag_ge(p.peer_res_flags[p.rank] + lin, p.round, env, SITE_AR_RESULT, lin);
         // all comm threads learn the outcome; also orders their loads after the acquire
@@ -1063,6 +1147,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         named_bar_sync(1, kCommThreads);
         ok = s_flags[1] != 0;
         named_bar_sync(1, kCommThreads);
+        const uint64_t tb1 = cprof ? globaltimer_ns() : 0;
+        if (cprof) {
+          acc_bw += tb1 - tb0;
+          prof[PROF_TL_COL_SEEN] = tb1 - t_kernel0;
+        }
         if (!ok || p.res_is_c) continue;
         const int rows = min(BM, p.M - mt * BM);
         const int cols = min(BN, p.N - nt * BN);
@@ -1092,6 +1181,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             }
           }
         }
+        if (cprof) acc_bc += globaltimer_ns() - tb1;
+      }
+      if (cprof) {
+        prof[PROF_AR_B_WAIT] = acc_bw;
+        prof[PROF_AR_B_COPY] = acc_bc;
       }
     }
   }

@@ -224,4 +224,72 @@ void spot_verify_launch(int64_t a, int64_t b, int64_t c, int M, int N, int K, in
   launch_count_add(1);
 }
 
+// ----------------------------------------------------------------------------
+// multimem transport probe: reduce-load 16-byte pieces of [begin, end) through the switch and
+// write them back (replicated through the switch, or to local memory). No waits, no flags:
+// ranks run it side by side on disjoint ranges. Reads how throughput depends on the number of
+// threads, the pieces each thread keeps in flight and the ordering qualifier.
+// ----------------------------------------------------------------------------
+template <int kU, bool kWeak, bool kLocalStore>
+__global__ void multimem_probe_kernel(const uint8_t* __restrict__ mc_in, uint8_t* __restrict__ mc_out,
+                                      uint8_t* __restrict__ local_out, int64_t begin, int64_t end) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < end;
+       i0 += stride * kU) {
+    uint4 v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end) {
+        if constexpr (kWeak)
+          asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                       : "l"(mc_in + i * 16)
+                       : "memory");
+        else
+          v[u] = multimem_ld_reduce_add_v4<true>(mc_in + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end) {
+        if constexpr (kLocalStore) {
+          st_global_v4(local_out + i * 16, v[u]);
+        } else if constexpr (kWeak) {
+          asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_out + i * 16),
+                       "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
+                       : "memory");
+        } else {
+          multimem_st_v4(mc_out + i * 16, v[u]);
+        }
+      }
+    }
+  }
+}
+
+void multimem_probe_launch(int64_t mc_in, int64_t mc_out, int64_t local_out, int64_t begin, int64_t end,
+                           int blocks, int threads, int unroll, bool weak, bool local_store,
+                           void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (blocks < 1 || threads < 32 || threads > 1024) throw std::runtime_error("tridist_b200: bad probe launch shape");
+  auto* in = reinterpret_cast<const uint8_t*>(mc_in);
+  auto* out = reinterpret_cast<uint8_t*>(mc_out);
+  auto* lo = reinterpret_cast<uint8_t*>(local_out);
+#define TDB_PROBE(U_)                                                                              \
+  do {                                                                                             \
+    if (weak && local_store) multimem_probe_kernel<U_, true, true><<<blocks, threads, 0, stream>>>(in, out, lo, begin, end);   \
+    else if (weak) multimem_probe_kernel<U_, true, false><<<blocks, threads, 0, stream>>>(in, out, lo, begin, end);           \
+    else if (local_store) multimem_probe_kernel<U_, false, true><<<blocks, threads, 0, stream>>>(in, out, lo, begin, end);    \
+    else multimem_probe_kernel<U_, false, false><<<blocks, threads, 0, stream>>>(in, out, lo, begin, end);                    \
+  } while (0)
+  if (unroll == 1) TDB_PROBE(1);
+  else if (unroll == 4) TDB_PROBE(4);
+  else if (unroll == 8) TDB_PROBE(8);
+  else throw std::runtime_error("tridist_b200: probe unroll must be 1, 4 or 8");
+#undef TDB_PROBE
+  check(cudaGetLastError(), "multimem_probe launch");
+  launch_count_add(1);
+}
+
 }  // namespace tdb

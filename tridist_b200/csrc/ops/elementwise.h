@@ -27,4 +27,9 @@ void spot_verify_launch(int64_t a, int64_t b, int64_t c, int M, int N, int K, in
                         int64_t ldb, int64_t ldc, bool bf16, int spots, float tol,
                         int64_t bad_tiles, int bn, void* stream);
 
+// Transport probe for the NVSwitch multicast path (see the kernel): pieces are 16 bytes,
+// [begin, end) counts pieces; `mc_in` / `mc_out` are multicast addresses.
+void multimem_probe_launch(int64_t mc_in, int64_t mc_out, int64_t local_out, int64_t begin, int64_t end,
+                           int blocks, int threads, int unroll, bool weak, bool local_store, void* stream);
+
 }  // namespace tdb

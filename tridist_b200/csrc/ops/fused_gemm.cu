@@ -109,6 +109,12 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     throw std::runtime_error("tridist_b200: GEMM+RS / GEMM+AR need N % 128 == 0");
   if (d.op == OP_AR2 && d.R > 1 && d.ldc % 8 != 0)
     throw std::runtime_error("tridist_b200: GEMM+AR needs a 16-byte aligned row stride of c");
+  if (d.nvls && d.op == OP_AR2 && d.R > 1) {
+    if (d.slot_stride != 0) throw std::runtime_error("tridist_b200: switch-reduced all-reduce keeps partials local (slot_stride = 0)");
+    for (int par = 0; par < 2; ++par)
+      if (d.mc_part[par] == 0 || d.mc_res[par] == 0 || d.mc_part[par] % 16 != 0 || d.mc_res[par] % 16 != 0)
+        throw std::runtime_error("tridist_b200: switch-reduced all-reduce needs 16-byte aligned multicast addresses");
+  }
   if (d.K % 8 != 0) throw std::runtime_error("tridist_b200: K must be a multiple of 8");
   if (d.N % 8 != 0) throw std::runtime_error("tridist_b200: N must be a multiple of 8");
   auto* plan = new GemmPlan();
@@ -160,6 +166,9 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
     p.res_is_c = d.res_is_c;
+    p.nvls = (d.nvls && d.op == OP_AR2 && d.R > 1) ? 1 : 0;
+    p.mc_part = reinterpret_cast<void*>(d.mc_part[par]);
+    p.mc_res = reinterpret_cast<void*>(d.mc_res[par]);
     for (int r = 0; r < d.R; ++r) {
       p.peer_ws[r] = reinterpret_cast<void*>(d.peer_ws[par][r]);
       p.peer_ag_flags[r] = reinterpret_cast<uint32_t*>(d.peer_ag_flags[r]);
@@ -186,6 +195,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.env.status = reinterpret_cast<StatusBlock*>(d.status_dev);
     p.env.abort_word = reinterpret_cast<uint32_t*>(d.abort_word);
     p.env.timeout_ns = d.timeout_ns;
+    p.env.poll_ns = d.poll_ns;
     p.env.rank = static_cast<uint32_t>(d.rank);
   }
   {

@@ -41,11 +41,18 @@ struct GemmPlanDesc {
   int64_t peer_res[2][8] = {};
   int64_t peer_res_flags[8] = {};
   int res_is_c = 0;
+  // two-shot all-reduce through the switch (multimem): multicast addresses, by parity, of the
+  // partial and result buffers; peer_slots then holds this rank's own partial buffer in every
+  // entry and slot_stride is 0
+  int nvls = 0;
+  int64_t mc_part[2] = {};
+  int64_t mc_res[2] = {};
   // failure reporting
   int64_t prof = 0;       // optional uint64 [grid][16] stall accounting (see ProfSlot)
   int64_t status_dev = 0;
   int64_t abort_word = 0;
   uint64_t timeout_ns = 2000000000ull;
+  uint32_t poll_ns = 0;   // pause between two polls of a cross-rank flag
 };
 
 int64_t gemm_plan_create(const GemmPlanDesc& d);

@@ -60,7 +60,7 @@ moe_meta_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restrict__ 
     d.splits[e] = hist[e];
     d.counters[e] = 0;
   }
-  __threadfence_system();
+  // the barrier orders every thread's stores before the releases below (cumulative)
   __syncthreads();
   if (tid < R) {
     st_release_sys(d.peer_meta_flags[tid] + d.rank, d.round);
@@ -141,16 +141,21 @@ moe_dispatch_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restric
     }
     for (; i < n16; i += 32) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
   }
-  __threadfence_system();
+  // one system fence per CTA, by the thread that counts the CTA in, after the barrier that
+  // orders all of the CTA's row stores before it (a fence in every thread costs microseconds)
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const uint32_t old = atomicAdd(d.done_counter, 1u);
     s_last = (old + 1u == static_cast<uint32_t>(ncta)) ? 1 : 0;
   }
   __syncthreads();
   if (s_last) {
-    if (tid == 0) atomicExch(d.done_counter, 0u);
-    __threadfence_system();
+    if (tid == 0) {
+      atomicExch(d.done_counter, 0u);
+      __threadfence_system();
+    }
+    __syncthreads();
     if (tid < d.R) {
       st_release_sys(d.peer_done_flags[tid] + d.rank, d.round);
       wait_flag_ge(d.peer_done_flags[d.rank] + tid, d.round, d.env, SITE_MOE_DISPATCH_DONE, tid);

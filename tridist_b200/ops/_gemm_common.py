@@ -80,18 +80,23 @@ class PlanCache:
 
 
 PROF_SLOTS = ["load_flag_wait", "load_empty_wait", "mma_full_wait", "mma_tmem_wait", "epi_busy", "epi_publish",
-              "epi_ticket_wait", "epi_tiles", "comm_total", "kernel"]
+              "epi_ticket_wait", "epi_tiles", "comm_total", "kernel", "ar_owner_wait", "ar_owner_work",
+              "ar_collect_wait", "ar_collect_copy", "epi_done_at", "ar_owner_done_at",
+              # time stamps (since the CTA started) of the last tile each role handled
+              "tl_acc_ready", "tl_staged", "tl_stored", "tl_flagged", "tl_own_seen", "tl_own_loaded",
+              "tl_own_fenced", "tl_own_flagged", "tl_col_seen", "tl_comm_start", "tl_own_it0"]
+PROF_WIDTH = 32
 _prof_buf: Optional[torch.Tensor] = None
 
 
 def prof_buffer() -> Optional[torch.Tensor]:
-    """Stall-accounting plane of the fused GEMM kernels ([CTA][16] int64 ns sums), allocated when
+    """Stall-accounting plane of the fused GEMM kernels ([CTA][32] int64 ns sums and stamps), allocated when
     ``TRIDIST_PROF=1``; plans created afterwards write into it."""
     global _prof_buf
     if not env_int("TRIDIST_PROF", 0):
         return None
     if _prof_buf is None:
-        _prof_buf = torch.zeros((256, 16), dtype=torch.int64, device="cuda")
+        _prof_buf = torch.zeros((256, PROF_WIDTH), dtype=torch.int64, device="cuda")
     return _prof_buf
 
 
@@ -105,7 +110,14 @@ def read_prof(n_ctas: int = 148) -> Dict[str, Dict[str, float]]:
     for i, name in enumerate(PROF_SLOTS):
         col = t[:, i]
         scale = 1.0 if name == "epi_tiles" else 1e-3
-        out[name] = {"mean": round(float(col.mean()) * scale, 2), "max": round(float(col.max()) * scale, 2)}
+        if name.startswith("tl_") or name.endswith("_at"):
+            nz = col[col > 0]                     # stamps: only CTAs that had such a tile
+            if nz.numel() == 0:
+                continue
+            out[name] = {"min": round(float(nz.min()) * scale, 2), "mean": round(float(nz.mean()) * scale, 2),
+                         "max": round(float(nz.max()) * scale, 2)}
+        else:
+            out[name] = {"mean": round(float(col.mean()) * scale, 2), "max": round(float(col.max()) * scale, 2)}
     return out
 
 
@@ -116,7 +128,7 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              M=M, N=N, K=K, a=a.data_ptr(), a_rows=a.shape[0], lda=a.stride(0),
              b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
              status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
-             max_ctas=env_int("TRIDIST_MAX_CTAS", 0),
+             max_ctas=env_int("TRIDIST_MAX_CTAS", 0), poll_ns=env_int("TRIDIST_POLL_NS", 0),
              prof=(prof_buffer().data_ptr() if prof_buffer() is not None else 0),
              allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and getattr(world, "kind", "") != "emulated") else 0)
     return d

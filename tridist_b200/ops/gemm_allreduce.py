@@ -14,13 +14,24 @@ one-shot  every epilogue stores its 16-bit partial tile into all ranks' slots an
           raises the tile ticket; every rank then sums the R partials of the tile
           in a fixed order (bit-identical result everywhere). One NVLink hop;
           best for small M (latency-bound decode shapes).
-two-shot  tile t is owned by rank t % R. Non-owners store their partial into the
-          owner's slot; the owner's epilogue adds them to its fp32 accumulator and
-          broadcasts the reduced tile into every rank's result buffer. 2(R-1)/R of
+two-shot  tile t is owned by rank t % R. Every rank stores its partial into the
+          owner's slot; the owner's communication warps add the R partials in fp32 and
+          broadcast the reduced tile into every rank's result buffer. 2(R-1)/R of
           the one-shot traffic; best for large M.
-
-An NVLS (multimem) variant is not built: the symmetric heap here is CUDA-IPC
-based and has no multicast binding.
+nvls      two-shot with the NVSwitch doing the arithmetic: partial tiles stay in the
+          producing rank's own memory, the owner reads the SUM of the R copies with
+          ``multimem.ld_reduce`` (added inside the switch, fp32 accumulation) and writes the
+          result to all ranks with one ``multimem.st``. Per rank (R-1)/R + 1/R of the
+          data leaves the GPU instead of 2(R-1)/R, and no SM adds anything. Needs a
+          multicast-capable buffer (``ProcessWorld.alloc_multicast``), which the context
+          allocates by default at three or more ranks (``nvls=False``, ``TRIDIST_NVLS=0``
+          or a fabric without multicast support leave it out) and checks once with known
+          integers before use. With it, ``auto`` takes this path for every size
+          (``TRIDIST_AR_NVLS_MIN_BYTES`` raises the threshold): at 4 GPUs it is ahead of
+          both peer-store algorithms from M = 128 to M = 4096 (K 28672, N 8192). At two
+          ranks one-shot moves the same bytes with one hop less and stays the choice.
+          The summation order inside the switch is not specified, but each tile is
+          reduced once, by its owner, so all ranks still hold bit-identical results.
 """
 from __future__ import annotations
 
@@ -51,6 +62,7 @@ class GemmARContext:
     res: Optional[SymmBuffer] = None         # [2][max_M, N] reduced result (two-shot)
     tile_flags: Optional[SymmBuffer] = None  # u32 [R, max_tiles]
     res_flags: Optional[SymmBuffer] = None   # u32 [max_tiles]
+    mc: Optional[object] = None              # McBuffer [part 0 | part 1 | res 0 | res 1], each max_M * N
     flag_round: int = 0
     plans: PlanCache = field(default_factory=PlanCache)
     mode: str = "auto"
@@ -64,14 +76,18 @@ class GemmARContext:
         two-shot kernel deliver peers' reduced tiles straight into ``c`` (no copy)."""
         if parity is None:
             parity = (self.flag_round + 1) & 1
-        off = parity * self.max_M * self.N * 2
-        return self.res.tensor(self.output_dtype, (M, self.N), off, rank=self.rank)
+        plane = self.max_M * self.N * 2
+        if pick_mode(self, M) == "nvls":
+            return self.mc.tensor(self.output_dtype, (M, self.N), (2 + parity) * plane, rank=self.rank)
+        return self.res.tensor(self.output_dtype, (M, self.N), parity * plane, rank=self.rank)
 
 
 def create_gemm_ar_intra_node_context(max_M, N, input_dtype, output_dtype, rank, num_ranks, mpi=None,
                                       comm=None, M_PER_CHUNK=512, gemm_stream=None, ar_stream=None,
-                                      world=None):
-    """Collective. Allocates partial-slot, result and ticket planes on the symmetric heap."""
+                                      world=None, nvls: Optional[bool] = None):
+    """Collective. Allocates partial-slot, result and ticket planes on the symmetric heap, and
+    (``nvls``: True / False / None = as the environment says) the multicast-bound planes of the
+    switch-reduced algorithm."""
     assert input_dtype == output_dtype, "input and output dtype must match"
     M_PER_CHUNK = min(M_PER_CHUNK, max_M)
     assert max_M % M_PER_CHUNK == 0 and M_PER_CHUNK % 64 == 0 and N % 128 == 0
@@ -88,15 +104,68 @@ def create_gemm_ar_intra_node_context(max_M, N, input_dtype, output_dtype, rank,
         ctx.res = world.alloc(2 * max_M * N * 2, rank)
         ctx.tile_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)
         ctx.res_flags = world.alloc(ctx.max_tiles * 4, rank)
+        if nvls is None:
+            nvls = ctx.mode == "nvls" or (ctx.mode == "auto" and num_ranks >= 3)
+        if nvls:
+            ctx.mc = world.alloc_multicast(4 * max_M * N * 2)
+        if ctx.mc is not None and env_int("TRIDIST_NVLS_SELFTEST", 1):
+            _nvls_selftest(ctx)
+        if ctx.mode == "nvls" and ctx.mc is None:
+            raise RuntimeError("tridist_b200: TRIDIST_AR_MODE=nvls but no multicast buffer could be made: "
+                               + str(getattr(world, "multicast_unavailable", "not a multi-process world")))
     world.host_barrier()
     return ctx
+
+
+def _nvls_selftest(ctx) -> None:
+    """Collective. One small all-reduce of known integers through the switch path; if any rank
+    sees a wrong value or a kernel-reported failure, all ranks drop the multicast buffer together
+    and the context keeps to the peer-store algorithms."""
+    import torch.distributed as dist
+    world, R, rank = ctx.world, ctx.num_ranks, ctx.rank
+    M, K = min(ctx.max_M, 128), 64
+    dev = torch.device("cuda", world.device)
+    a = torch.full((M, K), float(rank + 1), dtype=ctx.input_dtype, device=dev)
+    b = torch.ones((ctx.N, K), dtype=ctx.input_dtype, device=dev)
+    expect = float(K * R * (R + 1) // 2)          # exact in fp16 and bf16 for R <= 8
+    why = ""
+    saved_mode = ctx.mode
+    try:
+        ctx.mode = "nvls"
+        for _ in range(2):                         # both parities
+            c = torch.empty((M, ctx.N), dtype=ctx.output_dtype, device=dev)
+            gemm_ar_intra_node_op(a, b, c, ctx)
+            torch.cuda.synchronize()
+            world.check()
+            bad = int((c.float() != expect).sum().item())
+            if bad:
+                why = f"{bad} of {c.numel()} values differ from {expect}"
+                break
+    except Exception as exc:
+        why = f"{type(exc).__name__}: {exc}"
+        try:
+            world.clear_status()
+        except Exception:
+            pass
+    ctx.mode = saved_mode
+    ctx.plans.clear()
+    verdicts = [None] * R
+    dist.all_gather_object(verdicts, why, group=world.group)
+    if any(verdicts):
+        world.multicast_unavailable = "self-test failed: " + "; ".join(
+            f"rank {r}: {v}" for r, v in enumerate(verdicts) if v)
+        world.free_multicast(ctx.mc)
+        ctx.mc = None
 
 
 def pick_mode(ctx, M: int) -> str:
     if ctx.num_ranks == 1:
         return "local"
-    if ctx.mode in ("one_shot", "two_shot"):
+    if ctx.mode in ("one_shot", "two_shot", "nvls"):
         return ctx.mode
+    if ctx.mc is not None and ctx.num_ranks >= 3 and \
+            M * ctx.N * 2 >= env_int("TRIDIST_AR_NVLS_MIN_BYTES", 0):
+        return "nvls"
     if ctx.num_ranks == 2:
         return "one_shot"        # same traffic as two-shot at two ranks, one hop less
     limit = env_int("TRIDIST_AR_ONE_SHOT_BYTES", 4 << 20)
@@ -109,16 +178,27 @@ def _plan(ctx, a, b, c, mode, parity):
     N = b.shape[0]
     bn = choose_bn(M, N)
     res_is_c = 0
-    if mode == "two_shot":
-        res_ptr = ctx.res.local_ptr + parity * ctx.max_M * ctx.N * 2
+    plane = ctx.max_M * ctx.N * 2
+    if mode in ("two_shot", "nvls"):
+        res_ptr = (ctx.res.local_ptr + parity * plane) if mode == "two_shot" else \
+            (ctx.mc.local_ptr + (2 + parity) * plane)
         res_is_c = 1 if (c.data_ptr() == res_ptr and c.stride(0) == N) else 0
     key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), b.stride(0), c.stride(0),
            a.dtype, bn, mode, res_is_c, parity if res_is_c else -1)
 
     def make():
-        op = {"local": OP_PLAIN, "gemm": OP_PLAIN, "one_shot": OP_AR1, "two_shot": OP_AR2}[mode]
+        op = {"local": OP_PLAIN, "gemm": OP_PLAIN, "one_shot": OP_AR1, "two_shot": OP_AR2,
+              "nvls": OP_AR2}[mode]
         d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, op)
-        if op in (OP_AR1, OP_AR2):
+        if mode == "nvls":
+            # partials stay here: every "slot" entry is this rank's own partial plane
+            d["nvls"] = 1
+            d["peer_slots"] = [[ctx.mc.local_ptr] * R, [ctx.mc.local_ptr + plane] * R]
+            d["slot_stride"] = 0
+            d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + plane]
+            d["mc_res"] = [ctx.mc.mc_ptr + 2 * plane, ctx.mc.mc_ptr + 3 * plane]
+            d["peer_tile_flags"] = ctx.tile_flags.ptrs()
+        elif op in (OP_AR1, OP_AR2):
             half = R * ctx.max_M * ctx.N * 2
             d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
             d["slot_stride"] = M * N
@@ -127,8 +207,10 @@ def _plan(ctx, a, b, c, mode, parity):
             d["sched"] = SCHED_STRIDED
             d["seg_order"] = rotation_order(rank, R, 1, own_last=True)
             d["strided_interleave"] = 0 if env_str("TRIDIST_AR2_ORDER", "interleave") == "own_last" else 1
-            rhalf = ctx.max_M * ctx.N * 2
-            d["peer_res"] = [ctx.res.ptrs(0), ctx.res.ptrs(rhalf)]
+            if mode == "nvls":
+                d["peer_res"] = [ctx.mc.ptrs(2 * plane), ctx.mc.ptrs(3 * plane)]
+            else:
+                d["peer_res"] = [ctx.res.ptrs(0), ctx.res.ptrs(plane)]
             d["peer_res_flags"] = ctx.res_flags.ptrs()
             d["res_is_c"] = res_is_c
         return native().gemm_plan_create(d)
@@ -175,7 +257,7 @@ def gemm_ar_intra_node(a, b, ctx):
     """Allocating wrapper. With the two-shot algorithm the returned tensor is a view of the
     context's symmetric result buffer (valid until the second next call on this context)."""
     M = a.shape[0]
-    if (not isinstance(ctx.world, CpuWorld)) and pick_mode(ctx, M) == "two_shot":
+    if (not isinstance(ctx.world, CpuWorld)) and pick_mode(ctx, M) in ("two_shot", "nvls"):
         c = ctx.symm_output(M)
     else:
         c = torch.empty((M, b.shape[0]), dtype=ctx.output_dtype, device=a.device)
@@ -194,6 +276,9 @@ def gemm_ar_emulated(ctxs, a_list, b_list, c_list, mode="one_shot"):
 
 def finalize_gemm_ar_context(ctx) -> None:
     ctx.plans.clear()
+    if ctx.mc is not None:
+        ctx.world.free_multicast(ctx.mc)
+        ctx.mc = None
     if ctx.slots is not None and not isinstance(ctx.world, EmulatedWorld):
         for buf in (ctx.slots, ctx.res, ctx.tile_flags, ctx.res_flags):
             ctx.world.free(buf)

@@ -87,6 +87,14 @@ class SymmBuffer:
         return [p + byte_offset for p in self.peer_ptrs]
 
 
+@dataclass
+class McBuffer(SymmBuffer):
+    """A symmetric buffer with an NVSwitch multicast mapping: ``mc_ptr`` addresses all ranks'
+    copies at once (``multimem.*`` instructions only)."""
+    mc_ptr: int = 0
+    _keep: object = field(default=None, repr=False)
+
+
 class _WorldBase:
     kind = "base"
     rank: int
@@ -95,11 +103,22 @@ class _WorldBase:
     def __init__(self):
         self._barrier_ticket = 0
         self._buffers: List[SymmBuffer] = []
+        self._mc_buffers: List["McBuffer"] = []
         self.timeout_ms = env_int("TRIDIST_WAIT_TIMEOUT_MS", 4000)
 
     @property
     def timeout_ns(self) -> int:
         return int(self.timeout_ms) * 1_000_000
+
+    def alloc_multicast(self, nbytes: int):
+        """Worlds without an NVSwitch multicast mapping (one process, CPU) have none to give."""
+        return None
+
+    def free_multicast(self, buf) -> None:
+        return None
+
+    def release_multicast(self) -> None:
+        return None
 
 
 class ProcessWorld(_WorldBase):
@@ -171,6 +190,61 @@ class ProcessWorld(_WorldBase):
         buf.freed = True
         if buf in self._buffers:
             self._buffers.remove(buf)
+
+    def alloc_multicast(self, nbytes: int) -> Optional["McBuffer"]:
+        """Collective. A symmetric buffer that is also bound to an NVSwitch multicast object, so
+        kernels can use ``multimem.ld_reduce`` / ``multimem.st`` on ``mc_ptr`` (in-switch reduction
+        and replication). The virtual-memory plumbing (allocation, handle exchange, multicast
+        bind) is torch's symmetric-memory allocator; the kernels are this package's own.
+
+        Returns None on every rank when any rank cannot have it: one GPU, ``TRIDIST_NVLS=0``,
+        no multicast support in the driver / fabric, or a failed rendezvous."""
+        if self.num_ranks < 2 or env_int("TRIDIST_NVLS", 1) == 0:
+            return None
+        tensor = handle = None
+        mc, ptrs, why = 0, [], ""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = self.group if self.group is not None else dist.group.WORLD
+            nbytes = (int(nbytes) + 255) // 256 * 256
+            tensor = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", self.device))
+            handle = symm_mem.rendezvous(tensor, group)
+            mc = int(handle.multicast_ptr or 0)
+            ptrs = [int(x) for x in handle.buffer_ptrs]
+            if mc == 0:
+                why = "no multicast address"
+            elif len(ptrs) != self.num_ranks or ptrs[self.rank] != tensor.data_ptr():
+                mc, why = 0, "unexpected peer pointer table"
+        except Exception as exc:          # missing API, unsupported driver, refused rendezvous
+            mc, why = 0, f"{type(exc).__name__}: {exc}"
+        oks = [None] * self.num_ranks
+        dist.all_gather_object(oks, bool(mc), group=self.group)
+        if not all(oks):
+            self.multicast_unavailable = why or "a peer has no multicast support"
+            del handle, tensor
+            return None
+        buf = McBuffer(nbytes=nbytes, rank=self.rank, peer_ptrs=ptrs, device=self.device, _owner=self,
+                       mc_ptr=mc, _keep=(tensor, handle))
+        self._mc_buffers.append(buf)
+        return buf
+
+    def release_multicast(self) -> None:
+        """Collective: unbind every live multicast buffer (call before a rank leaves, so that no
+        rank exits while its memory is still bound to a multicast object the others use)."""
+        for buf in list(self._mc_buffers):
+            self.free_multicast(buf)
+
+    def free_multicast(self, buf: Optional["McBuffer"]) -> None:
+        """Collective: every rank drops its mapping after all of them stopped using it."""
+        if buf is None or buf.freed:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        buf._keep = None
+        buf.freed = True
+        if buf in self._mc_buffers:
+            self._mc_buffers.remove(buf)
+        dist.barrier(group=self.group)
 
     # -- synchronisation -----------------------------------------------------
     def barrier_on_stream(self) -> None:
@@ -352,6 +426,7 @@ def finalize_runtime() -> None:
     if w is None:
         return
     if isinstance(w, (ProcessWorld, EmulatedWorld)):
+        w.release_multicast()
         for buf in list(w._buffers):
             w.free(buf)
         w.C.status_free(w.status_host)

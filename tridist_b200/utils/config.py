@@ -12,9 +12,13 @@ TRIDIST_CTA_PAIR          0: never run 256-wide tiles on CTA pairs (2-CTA tcgen0
 TRIDIST_PUSH_CTAS         CTAs that drive the all-gather push (default 32; 0 = all)
 TRIDIST_PUSH_SKIP         scheduling rounds the pushing CTAs sit out (default 1 on large problems)
 TRIDIST_PROF              1: collect per-CTA stall accounting of the fused GEMM kernels
-TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot"
+TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot" | "nvls"
 TRIDIST_AR_ONE_SHOT_BYTES size threshold (bytes of one rank's partial) below which
-                          the one-shot all-reduce is used (default 4 MiB)
+                          the one-shot all-reduce is used (default 4 MiB; peer-store algorithms)
+TRIDIST_NVLS              0: never bind buffers to an NVSwitch multicast object (default 1)
+TRIDIST_NVLS_SELFTEST     0: skip the known-integers check of the switch path at context creation
+TRIDIST_AR_NVLS_MIN_BYTES result size from which "auto" uses the switch-reduced all-reduce (default 0)
+TRIDIST_POLL_NS           pause between two polls of a cross-rank ticket (default 0: back to back)
 TRIDIST_VERIFY            1: spot-verify fused AG+GEMM results and repair flagged tiles
 TRIDIST_VERIFY_SPOTS      elements recomputed per tile (default 4)
 TRIDIST_VERIFY_TOL        relative tolerance of the spot check (default 2e-2)

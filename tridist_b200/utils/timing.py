@@ -9,6 +9,7 @@ from __future__ import annotations
 import statistics
 import subprocess
 import threading
+import time
 from typing import Callable, Dict, List, Optional
 
 import torch
@@ -68,10 +69,11 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 100):
+    def __init__(self, gpu_index: int = 0, period_ms: int = 50):
         self.gpu_index = gpu_index
         self.period_ms = period_ms
         self.lines: List[str] = []
+        self.stamps: List[float] = []      # host arrival time of each line (time.monotonic)
         self._proc = None
         self._thr = None
 
@@ -87,12 +89,17 @@ class ClockSampler:
 
         def pump():
             for line in self._proc.stdout:
+                self.stamps.append(time.monotonic())
                 self.lines.append(line.strip())
 
         self._thr = threading.Thread(target=pump, daemon=True)
         self._thr.start()
 
-    def stop(self) -> Dict:
+    def stop(self, window: Optional[tuple] = None) -> Dict:
+        """Stop sampling and summarise. ``window`` = (t0, t1) in ``time.monotonic()`` seconds keeps
+        only the samples that arrived inside it (the timed region); if the region was too short to
+        catch one, all samples since ``start()`` are used (start the sampler before the warm-up, so
+        that these were taken under the same load) and ``"window"`` says so."""
         if self._proc is not None:
             self._proc.terminate()
             try:
@@ -103,7 +110,14 @@ class ClockSampler:
                 self._thr.join(timeout=2)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        lines, where = self.lines, "all samples"
+        if window is not None:
+            inside = [ln for ln, ts in zip(self.lines, self.stamps) if window[0] <= ts <= window[1] + 0.05]
+            if inside:
+                lines, where = inside, "timed region"
+            else:
+                where = "warm-up + timed region (timed region shorter than one sampling period)"
+        for line in lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -116,4 +130,4 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": where}
