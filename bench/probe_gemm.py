@@ -37,6 +37,9 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--probe", default="0", help="comma list of pipeline probes: 0 = the GEMM, 1 = tensor-pipe "
+                    "ceiling (resident stages, no loads), 2 = operand-feed ceiling (loads, no MMAs)")
+    ap.add_argument("--sustain-s", type=float, default=0.0, help="also time a back-to-back loop this long")
     args = ap.parse_args()
     os.environ["TRIDIST_CTA_PAIR"] = str(args.pair)
 
@@ -80,15 +83,43 @@ def main():
             ts = sorted(x.elapsed_time(y) for x, y in ev)
             return ts[len(ts) // 2]
 
+        def sustained(fn):
+            """Back-to-back launches for about --sustain-s seconds (no flush): the power-capped rate."""
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 0
+            import time
+            t_end = time.monotonic() + args.sustain_s
+            e0.record()
+            while time.monotonic() < t_end:
+                for _ in range(20):
+                    fn()
+                n += 20
+                torch.cuda.synchronize()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
         flops = 2.0 * M * N * K * (2 if args.swiglu else 1)
-        t_ours = timed(lambda: gemm_nt(a, b, out=out, **kw))
         row = {"M": M, "N": N, "K": K, "dtype": args.dtype, "bn": args.bn or "auto", "pair": args.pair,
-               "ours_ms": round(t_ours, 4), "ours_tflops": round(flops / t_ours / 1e9, 1), "max_abs_err": err}
+               "max_abs_err": err}
+        for probe in [int(x) for x in args.probe.split(",")]:
+            tag = {0: "ours", 1: "mma_only", 2: "feed_only"}[probe]
+            fn = lambda: gemm_nt(a, b, out=out, probe=probe, **kw)  # noqa: E731
+            t = timed(fn)
+            row[tag + "_ms"] = round(t, 4)
+            row[tag + "_tflops"] = round(flops / t / 1e9, 1)
+            if args.sustain_s > 0:
+                ts = sustained(fn)
+                row[tag + "_sustained_tflops"] = round(flops / ts / 1e9, 1)
+        t_ours = row.get("ours_ms")
         if not args.no_cublas and not args.swiglu:
             t_ref = timed(lambda: torch.matmul(a, b.t(), out=out))
             row["cublas_ms"] = round(t_ref, 4)
             row["cublas_tflops"] = round(flops / t_ref / 1e9, 1)
-            row["ratio"] = round(t_ref / t_ours, 3)
+            if t_ours:
+                row["ratio"] = round(t_ref / t_ours, 3)
+            if args.sustain_s > 0:
+                row["cublas_sustained_tflops"] = round(flops / sustained(lambda: torch.matmul(a, b.t(), out=out)) / 1e9, 1)
         print(json.dumps(row), flush=True)
         out_rows.append(row)
 

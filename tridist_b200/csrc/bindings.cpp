@@ -95,6 +95,7 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   g.abort_word = get<int64_t>(d, "abort_word", 0);
   g.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
   g.poll_ns = get<uint32_t>(d, "poll_ns", 0u);
+  g.probe = get<int>(d, "probe", 0);
   return gemm_plan_create(g);
 }
 

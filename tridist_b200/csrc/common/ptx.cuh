@@ -346,6 +346,18 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
       : "r"(smem_u32(bar)), "r"(0u)
       : "memory");
 }
+// Arrive on the barrier at this offset inside CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n"
+      "}\n"
+      :
+      : "r"(smem_u32(bar)), "r"(cta)
+      : "memory");
+}
 // 2-D tiled load into this CTA's shared memory whose completion bytes are credited to
 // the barrier at the same offset in the pair's LEADER CTA (no multicast: each CTA of
 // the pair loads its own operand halves).

@@ -172,7 +172,11 @@ struct alignas(64) GemmParams {
   uint64_t* prof;
 
   WaitEnv env;
-  int32_t pad_[2];
+  // Pipeline probes (plain GEMM only; results are meaningless): 1 = tensor-pipe ceiling, the
+  // ring is filled once and every k-block re-multiplies resident stages without waiting for
+  // loads; 2 = operand-feed ceiling, every stage is loaded and released without any MMA.
+  int32_t probe;
+  int32_t pad_;
 };
 
 // ----------------------------------------------------------------------------
@@ -480,7 +484,16 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       uint64_t acc_a = 0, acc_b = 0;
       uint32_t ready_mask[kMaxRanks] = {0};   // chunks of each source already observed
       uint32_t pending = 0;                   // stages with a load in flight (bitmask)
+      int loads_issued = 0;
       bool ok = true;
+      // Everything the k-block loop needs lives in registers: the inline-asm statements below
+      // clobber memory, so a field read through `p` inside the loop would be re-loaded on
+      // every k-block, in the one thread whose latency paces the whole operand pipeline.
+      const int k_blocks = p.k_blocks;
+      const int probe = p.probe;
+      const bool swiglu = p.epi == EPI_SWIGLU;
+      const int up_row0 = p.swiglu_up_row0;
+      const CUtensorMap* const bmap = &p.tma_b;
       for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
         const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
@@ -518,7 +531,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             }
           }
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int b_row_pair = swiglu
+            ? (sub == 0 ? t.n_tile * (BN / 2) : up_row0 + t.n_tile * (BN / 2))
+            : n0 + sub * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (probe == 1) {
+            if (loads_issued >= TS::kStages) break;   // ring filled once, then idle
+            ++loads_issued;
+          }
           if (prof && !mbar_try_wait(&empty_bar[stage], phase ^ 1u)) {
             const uint64_t tw = globaltimer_ns();
             ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
@@ -534,23 +554,19 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             // the leader's barrier collects the bytes of both CTAs' loads
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * TS::kStageBytes);
             tma_load_2d_pair(sa, amap, &full_bar[stage], kb * BK, a_row);
-            const int b_row = (p.epi == EPI_SWIGLU)
-                ? (sub == 0 ? t.n_tile * (BN / 2) : p.swiglu_up_row0 + t.n_tile * (BN / 2))
-                : n0 + sub * (BN / 2);
-            tma_load_2d_pair(sb, &p.tma_b, &full_bar[stage], kb * BK, b_row);
+            tma_load_2d_pair(sb, bmap, &full_bar[stage], kb * BK, b_row_pair);
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], TS::kStageBytes);
             tma_load_2d(sa, amap, &full_bar[stage], kb * BK, a_row);
-            if (p.epi == EPI_SWIGLU) {
+            if (swiglu) {
               // gate rows and the matching up rows form one BN-wide virtual tile
-              tma_load_2d(sb, &p.tma_b, &full_bar[stage], kb * BK, t.n_tile * (BN / 2));
-              tma_load_2d(sb + (BN / 2) * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
-                          p.swiglu_up_row0 + t.n_tile * (BN / 2));
+              tma_load_2d(sb, bmap, &full_bar[stage], kb * BK, t.n_tile * (BN / 2));
+              tma_load_2d(sb + (BN / 2) * BK * 2, bmap, &full_bar[stage], kb * BK,
+                          up_row0 + t.n_tile * (BN / 2));
             } else {
 #pragma unroll
               for (int h = 0; h < BN / 128; ++h)
-                tma_load_2d(sb + h * 128 * BK * 2, &p.tma_b, &full_bar[stage], kb * BK,
-                            n0 + h * 128);
+                tma_load_2d(sb + h * 128 * BK * 2, bmap, &full_bar[stage], kb * BK, n0 + h * 128);
             }
           }
           pending |= 1u << stage;
@@ -586,7 +602,16 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       uint32_t stage = 0, phase = 0;
       uint64_t acc_f = 0, acc_t = 0;
       int it = 0;
+      int kblocks_done = 0;
       bool ok = true;
+      // registers only inside the k-block loop (see the producer warp); the operand descriptors
+      // of stage s are those of stage 0 plus s times the stage size in 16-byte units
+      const int k_blocks = p.k_blocks;
+      const int probe = p.probe;
+      const uint64_t da0 = umma_desc_k_sw128(smem_u32(ring));
+      const uint64_t db0 = umma_desc_k_sw128(smem_u32(ring) + TS::kABytes);
+      constexpr uint64_t kDescStage = static_cast<uint64_t>(TS::kStageBytes >> 4);
+      uint64_t da = da0, db = db0;
       for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
         const TileCoord t = tile_at(p, s_order, pos, sub);
         if (!t.valid) continue;
@@ -602,20 +627,28 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (prof && !mbar_try_wait(&full_bar[stage], phase)) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (probe == 1 && kblocks_done >= TS::kStages) {
+            // tensor-pipe ceiling: the stage was filled in the first pass and stays resident
+          } else if (prof && !mbar_try_wait(&full_bar[stage], phase)) {
             const uint64_t tw = globaltimer_ns();
             ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
             acc_f += globaltimer_ns() - tw;
-          } else {
+          } else if (!mbar_try_wait(&full_bar[stage], phase)) {
             ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
           }
           if (!ok) break;
+          if (probe != 0) {
+            ++kblocks_done;
+            if (probe == 2) {
+              // operand-feed ceiling: hand the stage straight back to the producer(s)
+              mbar_arrive(&empty_bar[stage]);
+              if constexpr (kCtaM == 2) mbar_arrive_cluster(&empty_bar[stage], 1u);
+              if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+          }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(ring + stage * TS::kStageBytes);
-          const uint32_t sb = sa + TS::kABytes;
-          const uint64_t da = umma_desc_k_sw128(sa);
-          const uint64_t db = umma_desc_k_sw128(sb);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // +32 bytes per K step inside the 128-byte swizzle row
@@ -629,7 +662,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           // frees the smem stage (in both CTAs of a pair) when these MMAs retire
           if constexpr (kCtaM == 2) umma_commit_pair_both(&empty_bar[stage]);
           else umma_commit(&empty_bar[stage]);
-          if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+          da += kDescStage;
+          db += kDescStage;
+          if (++stage == TS::kStages) { stage = 0; phase ^= 1u; da = da0; db = db0; }
         }
         if (!ok) break;
         // accumulator complete (each CTA of a pair reads its own 128 rows)

@@ -196,6 +196,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.env.abort_word = reinterpret_cast<uint32_t*>(d.abort_word);
     p.env.timeout_ns = d.timeout_ns;
     p.env.poll_ns = d.poll_ns;
+    p.probe = (d.op == OP_PLAIN && d.R == 1) ? d.probe : 0;
     p.env.rank = static_cast<uint32_t>(d.rank);
   }
   {

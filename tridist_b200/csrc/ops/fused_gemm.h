@@ -52,6 +52,7 @@ struct GemmPlanDesc {
   int64_t status_dev = 0;
   int64_t abort_word = 0;
   uint64_t timeout_ns = 2000000000ull;
+  int probe = 0;          // pipeline probes of the plain GEMM (see GemmParams::probe)
   uint32_t poll_ns = 0;   // pause between two polls of a cross-rank flag
 };
 

@@ -161,12 +161,14 @@ def plain_world():
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
-            bn: Optional[int] = None, swiglu: bool = False, max_ctas: int = 0) -> torch.Tensor:
+            bn: Optional[int] = None, swiglu: bool = False, max_ctas: int = 0, probe: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` on the hand-written tcgen05 kernel (fp32 accumulate).
 
     With ``swiglu=True`` b holds ``[gate; up]`` row blocks (2*I rows) and the
     result is ``silu(a @ gate.T) * (a @ up.T)`` of shape [M, I], computed in the
-    GEMM epilogue.
+    GEMM epilogue. ``probe`` = 1 / 2 runs the pipeline probes (tensor-pipe ceiling: resident
+    stages re-multiplied without loads; operand-feed ceiling: loads without MMAs); the output
+    is then meaningless.
     """
     assert a.is_cuda and b.is_cuda and a.dtype == b.dtype
     M, K = a.shape
@@ -179,7 +181,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         bn = choose_bn(M, N, swiglu)
     w = plain_world()
     key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
-           out.stride(0), bn, swiglu, a.dtype, max_ctas)
+           out.stride(0), bn, swiglu, a.dtype, max_ctas, probe)
 
     def make():
         d = base_desc(w, 0, 1, a, b, out.data_ptr(), out.stride(0), M, N, K, bn, OP_PLAIN)
@@ -188,6 +190,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
             d["swiglu_up_row0"] = N
         if max_ctas:
             d["max_ctas"] = max_ctas
+        d["probe"] = probe
         return native().gemm_plan_create(d)
 
     pid = _plain_cache.get(key, make)
