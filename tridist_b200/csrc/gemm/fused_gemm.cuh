@@ -877,16 +877,22 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool finalizes =
           tile_has_rows && (!multi || p.op == OP_PLAIN || p.op == OP_AG || tile_reduces);
       if (finalizes) {
+        // registers only inside the column loop: its inline-asm statements clobber memory, so
+        // fields read through `p` there would be re-loaded for every 32-column chunk
+        const int op = p.op;
+        const bool swiglu = p.epi == EPI_SWIGLU;
+        const int n_cols = p.N;
+        uint8_t* const c_base = reinterpret_cast<uint8_t*>(p.c);
+        const bool local_tile = !multi || op == OP_PLAIN || op == OP_AG;
         for (int c = 0; c < BN / 32; ++c) {
-          if (p.epi == EPI_SWIGLU && c >= BN / 64) break;
-          const int ocol = (p.epi == EPI_SWIGLU) ? t.n_tile * (BN / 2) + c * 32
-                                                 : t.n_tile * BN + c * 32;
+          if (swiglu && c >= BN / 64) break;
+          const int ocol = swiglu ? t.n_tile * (BN / 2) + c * 32 : t.n_tile * BN + c * 32;
           float acc[32];
-          if (multi && p.op == OP_AR1) {
+          if (multi && op == OP_AR1) {
             // all R contributions (own included) are summed from their 16-bit form
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-          } else if (p.epi == EPI_SWIGLU) {
+          } else if (swiglu) {
             // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
             uint32_t g[32], u[32];
             tmem_ld_32x32b_x32(taddr + c * 32, g);
@@ -902,13 +908,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r[j]);
           }
-          const bool active = row_ok && ocol < p.N;
+          const bool active = row_ok && ocol < n_cols;
           if (active) {
-            if (!multi || p.op == OP_PLAIN || p.op == OP_AG) {
-              store_row32<kBf16>(reinterpret_cast<uint8_t*>(p.c) +
-                                     (static_cast<int64_t>(row) * ldc + ocol) * 2,
-                                 acc);
-            } else if (p.op == OP_RS) {
+            if (local_tile) {
+              store_row32<kBf16>(c_base + (static_cast<int64_t>(row) * ldc + ocol) * 2, acc);
+            } else if (op == OP_RS) {
               if (owner == p.rank) {
                 const int lrow = row - owner * p.m_per_rank;
                 // fixed source order keeps the sum deterministic
@@ -920,8 +924,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                                        (static_cast<int64_t>(lrow) * ldc + ocol) * 2,
                                    acc);
               }
-            } else if (p.op == OP_AR1) {
-              const int64_t off = static_cast<int64_t>(row) * p.N + ocol;
+            } else if (op == OP_AR1) {
+              const int64_t off = static_cast<int64_t>(row) * n_cols + ocol;
               add_rows32_from_sources<kBf16>(
                   acc, reinterpret_cast<const uint8_t*>(p.peer_slots[p.rank]) + off * 2,
                   p.slot_stride * 2, p.R, -1);
