@@ -1,0 +1,65 @@
+"""Host-side decisions that need no GPU: all-reduce algorithm choice, clock-sample windows,
+worlds without a multicast mapping, and the reference's import paths."""
+import types
+
+import pytest
+import torch
+
+
+def _ar_ctx(R, mode="auto", mc=None, max_M=4096, N=8192):
+    from tridist_b200.ops.gemm_allreduce import GemmARContext
+    return GemmARContext(rank=0, num_ranks=R, max_M=max_M, N=N, input_dtype=torch.float16,
+                         output_dtype=torch.float16, M_PER_CHUNK=64, world=None, mode=mode, mc=mc)
+
+
+def test_allreduce_mode_choice(monkeypatch):
+    from tridist_b200.ops.gemm_allreduce import pick_mode
+    for name in ("TRIDIST_AR_NVLS_MIN_BYTES", "TRIDIST_AR_ONE_SHOT_BYTES"):
+        monkeypatch.delenv(name, raising=False)
+    assert pick_mode(_ar_ctx(1), 128) == "local"
+    assert pick_mode(_ar_ctx(2), 4096) == "one_shot"                  # same bytes, one hop less
+    assert pick_mode(_ar_ctx(8), 128) == "one_shot"                   # 2 MiB partial, no multicast buffer
+    assert pick_mode(_ar_ctx(8), 4096) == "two_shot"
+    mc = types.SimpleNamespace(mc_ptr=1 << 40)
+    assert pick_mode(_ar_ctx(8, mc=mc), 128) == "nvls"
+    assert pick_mode(_ar_ctx(2, mc=mc), 4096) == "one_shot"           # two ranks never go through the switch
+    assert pick_mode(_ar_ctx(8, mode="two_shot", mc=mc), 4096) == "two_shot"   # explicit mode wins
+    monkeypatch.setenv("TRIDIST_AR_NVLS_MIN_BYTES", str(8 << 20))
+    assert pick_mode(_ar_ctx(8, mc=mc), 128) == "one_shot"            # below the switch threshold
+    assert pick_mode(_ar_ctx(8, mc=mc), 4096) == "nvls"
+
+
+def test_clock_sampler_window():
+    from tridist_b200.utils.timing import ClockSampler
+    s = ClockSampler(0)
+    row = "0, {}, 1965, 900.0, 0x4, Not Active, Not Active, Not Active, {}"
+    s.lines = [row.format(600, "Not Active"), row.format(1400, "Active"), row.format(1500, "Active"),
+               row.format(700, "Not Active")]
+    s.stamps = [1.0, 2.0, 2.5, 4.0]
+    inside = s.stop(window=(1.9, 2.6))
+    assert inside["samples"] == 2 and inside["sm_mhz"] == 1450.0 and inside["reasons"] == ["sw_power_cap"]
+    assert inside["window"] == "timed region"
+    short = s.stop(window=(2.1, 2.2))            # nothing arrived inside: fall back to everything since start()
+    assert short["samples"] == 4 and "warm-up" in short["window"]
+    assert s.stop()["samples"] == 4
+
+
+def test_worlds_without_multicast():
+    from tridist_b200.parallel.runtime import CpuWorld
+    w = CpuWorld(0, 1)
+    assert w.alloc_multicast(1 << 20) is None
+    w.release_multicast()                        # no-op, must not raise
+
+
+def test_reference_import_paths():
+    import pydushmem
+    import triton_dist.kernels.dcu as dcu
+    from triton_dist.kernels.dcu import gemm_allreduce, i1_predictor, moe_a2a
+    import tridist_b200.ops as ops
+    assert dcu.ag_gemm_intra_node_op is ops.ag_gemm_intra_node_op
+    assert gemm_allreduce.gemm_ar_intra_node is ops.gemm_ar_intra_node
+    assert moe_a2a.moe_dispatch_intra_node_op is ops.moe_dispatch_intra_node_op
+    assert i1_predictor.StickyOrderPredictor is ops.StickyOrderPredictor
+    assert pydushmem.host.mpi_comm_size() >= 1
+    for name in ("malloc", "ptr", "putmem", "getmem", "barrier_all", "my_pe", "n_pes"):
+        assert callable(getattr(pydushmem, name))

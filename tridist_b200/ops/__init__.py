@@ -19,3 +19,5 @@ from .gemm_ar_rd import (create_gemm_ar_rd_context, finalize_gemm_ar_rd_context,
                          gemm_ar_rd_op)
 from .gemm_rs_v5 import (create_gemm_rs_v5_context, finalize_gemm_rs_v5_context, gemm_rs_v5,  # noqa: F401
                          gemm_rs_v5_op)
+# the arrival-order predictor of the skew layer (reference: triton_dist/kernels/dcu/i1_predictor.py:35)
+from ..parallel.predictor import StickyOrderPredictor, infer_straggler  # noqa: F401,E402
