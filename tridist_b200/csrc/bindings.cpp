@@ -33,7 +33,7 @@ static void fill_ptrs2(const py::dict& d, const char* k, int64_t (*out)[8]) {
     for (int i = 0; i < 8 && i < static_cast<int>(v[p].size()); ++i) out[p][i] = v[p][i];
 }
 
-static int64_t py_gemm_plan_create(const py::dict& d) {
+static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   GemmPlanDesc g;
   g.op = get<int>(d, "op", 0);
   g.epi = get<int>(d, "epi", 0);
@@ -96,7 +96,13 @@ static int64_t py_gemm_plan_create(const py::dict& d) {
   g.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
   g.poll_ns = get<uint32_t>(d, "poll_ns", 0u);
   g.probe = get<int>(d, "probe", 0);
-  return gemm_plan_create(g);
+  return g;
+}
+
+static int64_t py_gemm_plan_create(const py::dict& d) { return gemm_plan_create(gemm_desc_from(d)); }
+
+static std::vector<std::vector<std::array<int, 5>>> py_schedule_dump(const py::dict& d, int sms) {
+  return schedule_dump(gemm_desc_from(d), sms);
 }
 
 static MoeDesc moe_desc_from(const py::dict& d) {
@@ -212,6 +218,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     multimem_probe_launch(mc_in, mc_out, local_out, begin, end, blocks, threads, unroll, weak, local_store,
                           cur_stream());
   });
+  m.def("schedule_dump", &py_schedule_dump, py::arg("desc"), py::arg("sms") = 148);
   m.def("spot_verify", [](int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           bool bf16, int spots, float tol, int64_t bad_tiles, int bn) {
     spot_verify_launch(a, b, c, M, N, K, lda, ldb, ldc, bf16, spots, tol, bad_tiles, bn, cur_stream());

@@ -187,7 +187,7 @@ struct TileCoord {
   bool valid;
 };
 
-__device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, int& mt, int& nt) {
+__host__ __device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, int& mt, int& nt) {
   // Groups of 8 m-tiles walked column by column: a wave of CTAs shares few A
   // row blocks and a contiguous run of B column blocks in L2.
   constexpr int G = 8;
@@ -204,7 +204,7 @@ __device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, 
 // consecutive m-tiles (cta_m = 2 for CTA pairs; CTA `sub` of the pair owns m-tile
 // unit_m * cta_m + sub). `linear` indexes the tile's ticket words; `owner_key` is the
 // unit id that decides the owning rank in the strided (two-shot all-reduce) order.
-__device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos,
+__host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos,
                                              int sub) {
   TileCoord t;
   t.valid = true;
@@ -242,11 +242,40 @@ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t*
   return t;
 }
 
-__device__ __forceinline__ int sched_positions(const GemmParams& p) {
+__host__ __device__ __forceinline__ int sched_positions(const GemmParams& p) {
   const int total = p.unit_m * p.n_tiles;
   if (p.sched == SCHED_STRIDED) return ((total + p.R - 1) / p.R) * p.R;
   if (p.sched == SCHED_LIST) return p.list_len;
   return total;
+}
+
+// Static round-robin of the scheduling positions over the workers (a worker is a CTA, or a CTA
+// pair), with one twist: the workers that push the all-gather shard sit out the first `skip`
+// rounds (their copy engine is busy and their operand loads are slower meanwhile), so that all
+// workers finish together. Shared by the kernel and the host-side schedule dump.
+struct WorkerSchedule {
+  int workers;   // workers in the grid
+  int pushers;   // workers 0 .. pushers-1 drive the all-gather push
+  int skip;      // rounds the pushers sit out
+  int early;     // workers active in the early rounds
+  __host__ __device__ int pos_of(int my_worker, int i) const {
+    if (my_worker < pushers) return skip * early + i * workers + my_worker;
+    if (i < skip) return i * early + (my_worker - pushers);
+    return skip * early + (i - skip) * workers + my_worker;
+  }
+};
+__host__ __device__ __forceinline__ WorkerSchedule make_worker_schedule(const GemmParams& p, int grid_x,
+                                                                        int cta_m) {
+  WorkerSchedule w;
+  w.workers = grid_x / cta_m;
+  w.pushers = 0;
+  w.skip = 0;
+  if (p.op == OP_AG && p.R > 1 && !p.skip_comm && p.push_ctas > 0 && p.push_ctas < grid_x) {
+    w.pushers = (p.push_ctas + cta_m - 1) / cta_m;
+    w.skip = p.push_skip_rounds;
+  }
+  w.early = w.workers - w.pushers;
+  return w;
 }
 
 // ----------------------------------------------------------------------------
@@ -412,24 +441,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // TMEM-empty barriers the pair synchronises on).
   const int sub = (kCtaM == 2) ? static_cast<int>(cluster_ctarank()) : 0;
   const bool leader = sub == 0;
-  // Static round-robin over scheduling positions, with one twist: the CTAs that push the
-  // all-gather shard sit out the first `push_skip_rounds` rounds (their copy engine is busy
-  // and their operand loads are slower meanwhile), so that all CTAs finish together.
-  const int sched_workers = static_cast<int>(gridDim.x) / kCtaM;
+  const WorkerSchedule wsched = make_worker_schedule(p, static_cast<int>(gridDim.x), kCtaM);
   const int my_worker = static_cast<int>(blockIdx.x) / kCtaM;
-  int sched_pushers = 0, sched_skip = 0;
-  if (p.op == OP_AG && p.R > 1 && !p.skip_comm && p.push_ctas > 0 &&
-      p.push_ctas < static_cast<int>(gridDim.x)) {
-    sched_pushers = (p.push_ctas + kCtaM - 1) / kCtaM;
-    sched_skip = p.push_skip_rounds;
-  }
-  const int sched_early = sched_workers - sched_pushers;    // workers active in the early rounds
-  const bool i_push = my_worker < sched_pushers;
-  auto pos_of = [&](int i) -> int {
-    if (i_push) return sched_skip * sched_early + i * sched_workers + my_worker;
-    if (i < sched_skip) return i * sched_early + (my_worker - sched_pushers);
-    return sched_skip * sched_early + (i - sched_skip) * sched_workers + my_worker;
-  };
+  auto pos_of = [&](int i) -> int { return wsched.pos_of(my_worker, i); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TS::kStages; ++s) {

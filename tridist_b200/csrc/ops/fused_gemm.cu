@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <array>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -100,6 +101,73 @@ static void set_attr_once() {
   }
 }
 
+// CTA pairs (one 2-CTA tcgen05 MMA per 256 x 256 output tile) where the schedule allows.
+static int choose_cta_m(const GemmPlanDesc& d) {
+  const int mt = (d.M + BM - 1) / BM;
+  bool pair = d.allow_pair && d.bn == 256 && mt >= 2 && d.sched != SCHED_LIST;
+  if (d.sched == SCHED_SEGMENT && ((mt / d.R) % 2 != 0)) pair = false;
+  return pair ? 2 : 1;
+}
+
+// Everything the tile schedule depends on (shared by plan creation and the host-side dump).
+static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p) {
+  const int bn_out = (d.epi == EPI_SWIGLU) ? d.bn / 2 : d.bn;
+  p.M = d.M; p.N = d.N; p.K = d.K;
+  p.m_tiles = (d.M + BM - 1) / BM;
+  p.n_tiles = (d.N + bn_out - 1) / bn_out;
+  p.k_blocks = (d.K + BK - 1) / BK;
+  p.rank = d.rank; p.R = d.R;
+  p.op = d.op; p.epi = d.epi; p.sched = d.sched;
+  p.m_per_rank = d.m_per_rank > 0 ? d.m_per_rank : d.M;
+  p.cta_m = cta_m;
+  p.unit_m = (p.m_tiles + p.cta_m - 1) / p.cta_m;
+  p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? (p.m_tiles / d.R) / p.cta_m : p.unit_m;
+  if (d.sched == SCHED_SEGMENT && (p.m_tiles % d.R != 0 || p.m_per_rank % BM != 0))
+    throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
+  for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
+  p.strided_interleave = d.strided_interleave;
+  p.list_len = d.list_len;
+  p.swiglu_up_row0 = d.swiglu_up_row0;
+  p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;
+  p.n_chunks = d.n_chunks > 0 ? d.n_chunks : 1;
+  p.push_parts = d.push_parts > 0 ? d.push_parts : 1;
+  p.skip_comm = d.skip_comm;
+  p.push_ctas = d.push_ctas;
+  p.push_skip_rounds = d.push_skip_rounds;
+}
+
+// Persistent grid: one CTA (or CTA pair) per scheduling position, at most one per SM.
+static int grid_for(const GemmParams& p, int max_ctas, int sms) {
+  const int positions = sched_positions(p);
+  int g = max_ctas > 0 ? max_ctas : sms;
+  if (g > sms) g = sms;
+  g /= p.cta_m;                             // units that can run at once
+  int units = positions < g ? positions : g;
+  if (units < 1) units = 1;
+  return units * p.cta_m;
+}
+
+std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d, int sms) {
+  if (d.sched == SCHED_LIST) throw std::runtime_error("tridist_b200: a tile list is its own schedule");
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int cta_m = choose_cta_m(d);
+  fill_schedule_fields(d, cta_m, p);
+  const int grid_x = grid_for(p, d.max_ctas, sms);
+  const WorkerSchedule ws = make_worker_schedule(p, grid_x, cta_m);
+  const int positions = sched_positions(p);
+  std::vector<std::vector<std::array<int, 5>>> out(grid_x);
+  for (int cta = 0; cta < grid_x; ++cta) {
+    const int sub = cta % cta_m, worker = cta / cta_m;
+    for (int i = 0, pos = ws.pos_of(worker, 0); pos < positions; pos = ws.pos_of(worker, ++i)) {
+      const TileCoord t = tile_at(p, p.seg_order, pos, sub);
+      if (!t.valid) continue;
+      out[cta].push_back({t.m_tile, t.n_tile, t.linear, t.owner_key, pos});
+    }
+  }
+  return out;
+}
+
 int64_t gemm_plan_create(const GemmPlanDesc& d) {
   if (d.R < 1 || d.R > kMaxRanks) throw std::runtime_error("tridist_b200: 1 <= R <= 8 required");
   if (d.bn != 128 && d.bn != 256) throw std::runtime_error("tridist_b200: BN must be 128 or 256");
@@ -120,35 +188,13 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
   auto* plan = new GemmPlan();
   plan->bn = d.bn;
   plan->bf16 = d.bf16;
-  // CTA pairs (one 2-CTA tcgen05 MMA per 256 x 256 output tile) where the schedule allows
-  {
-    const int mt = (d.M + BM - 1) / BM;
-    bool pair = d.allow_pair && d.bn == 256 && mt >= 2 && d.sched != SCHED_LIST;
-    if (d.sched == SCHED_SEGMENT && ((mt / d.R) % 2 != 0)) pair = false;
-    plan->cta_m = pair ? 2 : 1;
-  }
-  const int bn_out = (d.epi == EPI_SWIGLU) ? d.bn / 2 : d.bn;
+  plan->cta_m = choose_cta_m(d);
   for (int par = 0; par < 2; ++par) {
     GemmParams& p = plan->prm[par];
     std::memset(&p, 0, sizeof(p));
-    p.M = d.M; p.N = d.N; p.K = d.K;
-    p.m_tiles = (d.M + BM - 1) / BM;
-    p.n_tiles = (d.N + bn_out - 1) / bn_out;
-    p.k_blocks = (d.K + BK - 1) / BK;
-    p.rank = d.rank; p.R = d.R;
-    p.op = d.op; p.epi = d.epi; p.sched = d.sched;
-    p.m_per_rank = d.m_per_rank > 0 ? d.m_per_rank : d.M;
-    p.cta_m = plan->cta_m;
-    p.unit_m = (p.m_tiles + p.cta_m - 1) / p.cta_m;
-    p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? (p.m_tiles / d.R) / p.cta_m : p.unit_m;
-    if (d.sched == SCHED_SEGMENT && (p.m_tiles % d.R != 0 || p.m_per_rank % BM != 0))
-      throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
-    for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
+    fill_schedule_fields(d, plan->cta_m, p);
     p.order_table = reinterpret_cast<const int32_t*>(d.order_table);
-    p.strided_interleave = d.strided_interleave;
     p.tile_list = reinterpret_cast<const int32_t*>(d.tile_list);
-    p.list_len = d.list_len;
-    p.swiglu_up_row0 = d.swiglu_up_row0;
     p.is_bf16 = d.bf16 ? 1 : 0;
     p.c = reinterpret_cast<void*>(d.c);
     p.ldc = d.ldc;
@@ -156,12 +202,6 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.tma_b = make_tmap(reinterpret_cast<void*>(d.b), d.b_rows, d.K, d.ldb, d.bf16);
     p.tma_a_ws = p.tma_a;
     p.a_local = reinterpret_cast<const void*>(d.a);
-    p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;
-    p.n_chunks = d.n_chunks > 0 ? d.n_chunks : 1;
-    p.push_parts = d.push_parts > 0 ? d.push_parts : 1;
-    p.skip_comm = d.skip_comm;
-    p.push_ctas = d.push_ctas;
-    p.push_skip_rounds = d.push_skip_rounds;
     p.ag_counters = reinterpret_cast<uint32_t*>(d.ag_counters);
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
@@ -199,18 +239,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.probe = (d.op == OP_PLAIN && d.R == 1) ? d.probe : 0;
     p.env.rank = static_cast<uint32_t>(d.rank);
   }
-  {
-    const GemmParams& p = plan->prm[0];
-    int positions = p.unit_m * p.n_tiles;
-    if (p.sched == SCHED_STRIDED) positions = ((positions + p.R - 1) / p.R) * p.R;
-    if (p.sched == SCHED_LIST) positions = p.list_len;
-    int g = d.max_ctas > 0 ? d.max_ctas : num_sms();
-    if (g > num_sms()) g = num_sms();
-    g /= plan->cta_m;                       // units that can run at once
-    int units = positions < g ? positions : g;
-    if (units < 1) units = 1;
-    plan->grid_x = units * plan->cta_m;
-  }
+  plan->grid_x = grid_for(plan->prm[0], d.max_ctas, num_sms());
   std::lock_guard<std::mutex> lk(g_mu);
   const int64_t id = g_next_plan++;
   g_plans[id] = plan;

@@ -1,5 +1,6 @@
 // Plain-C++ interface of the fused GEMM family (no torch / pybind types here).
 #pragma once
+#include <array>
 #include <cstdint>
 #include <cstring>
 #include <vector>
@@ -64,6 +65,11 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
 // Runs several ranks' plans as ONE cooperative kernel on one GPU (grid.y = rank).
 void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round, int parity,
                                 int skip_comm, void* stream);
+
+// Host-side replay of the kernel's tile schedule (same functions as the device code, no GPU
+// needed): for every CTA of the grid the tiles it would process, in order, as
+// {m_tile, n_tile, ticket index, owner key, scheduling position}. `sms` = SMs of the target GPU.
+std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d, int sms);
 
 int64_t launch_count();
 void launch_count_add(int64_t n);
