@@ -38,7 +38,7 @@ def reference_arm(args) -> None:
         "impl": "reference",
         "unavailable": "reference is DCU-only: it loads libdushmem_host.so/libamdhip64.so via ctypes and needs "
                        "Triton's hcu backend + DTK bitcode; it has no setup.py/pyproject to install and cannot "
-                       "run on CUDA (see DESIGN.md)"}))
+                       "run on CUDA"}))
 
 
 def main() -> None:
