@@ -17,7 +17,6 @@ import argparse
 import json
 import math
 import os
-import statistics
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -19,7 +19,7 @@ import torch
 from tridist_b200.models.tp_mlp import TPMLP, TPMLPConfig
 from tridist_b200.ops import (ag_gemm_intra_node_op, create_ag_gemm_intra_node_context,
                               create_gemm_ar_intra_node_context, create_gemm_rs_intra_node_context,
-                              create_moe_a2a_intra_node_context, gemm_ar_intra_node, gemm_ar_intra_node_op,
+                              create_moe_a2a_intra_node_context, gemm_ar_intra_node,
                               gemm_rs_intra_node_op, moe_combine_intra_node_op, moe_dispatch_intra_node_op)
 from tridist_b200.utils import roofline
 from tridist_b200.utils.testing import moe_inputs

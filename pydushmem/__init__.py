@@ -1,7 +1,6 @@
 """Import-path alias of the reference's host binding package: the one-sided host calls
 (``init / malloc / free / ptr / putmem / getmem / quiet / fence / barrier_all / my_pe / n_pes``) map onto
 tridist_b200.parallel.symm_host. There is no MPI here: ``host.mpi_init()`` returns placeholders."""
-from tridist_b200.parallel import symm_host as _sh
 from tridist_b200.parallel.symm_host import SymmHost, get_host, init  # noqa: F401
 
 from . import host  # noqa: F401,E402

@@ -2,7 +2,6 @@
 worlds without a multicast mapping, and the reference's import paths."""
 import types
 
-import pytest
 import torch
 
 

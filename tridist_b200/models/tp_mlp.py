@@ -16,7 +16,7 @@ epilogue and h is never written to memory.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 

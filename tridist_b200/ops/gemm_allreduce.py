@@ -44,7 +44,7 @@ from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ..utils.config import env_int, env_str
-from ._gemm_common import (BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_NATURAL, SCHED_STRIDED, PlanCache,
+from ._gemm_common import (BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_STRIDED, PlanCache,
                            base_desc, choose_bn, rotation_order)
 
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import os
 import socket
 import traceback
-from typing import Callable, List, Tuple
+from typing import Callable
 
 import torch
 import torch.distributed as dist
