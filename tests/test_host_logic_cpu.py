@@ -23,6 +23,9 @@ def test_allreduce_mode_choice(monkeypatch):
     assert pick_mode(_ar_ctx(8, mc=mc), 128) == "nvls"
     assert pick_mode(_ar_ctx(2, mc=mc), 4096) == "one_shot"           # two ranks never go through the switch
     assert pick_mode(_ar_ctx(8, mode="two_shot", mc=mc), 4096) == "two_shot"   # explicit mode wins
+    import pytest
+    with pytest.raises(RuntimeError):
+        pick_mode(_ar_ctx(8, mode="nvls"), 128)                      # asked for, but no multicast buffer
     monkeypatch.setenv("TRIDIST_AR_NVLS_MIN_BYTES", str(8 << 20))
     assert pick_mode(_ar_ctx(8, mc=mc), 128) == "one_shot"            # below the switch threshold
     assert pick_mode(_ar_ctx(8, mc=mc), 4096) == "nvls"

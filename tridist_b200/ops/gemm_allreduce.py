@@ -161,6 +161,9 @@ def _nvls_selftest(ctx) -> None:
 def pick_mode(ctx, M: int) -> str:
     if ctx.num_ranks == 1:
         return "local"
+    if ctx.mode == "nvls" and ctx.mc is None:
+        raise RuntimeError("tridist_b200: mode 'nvls' needs a context created with a multicast buffer "
+                           "(nvls=True on a fabric with multicast support)")
     if ctx.mode in ("one_shot", "two_shot", "nvls"):
         return ctx.mode
     if ctx.mc is not None and ctx.num_ranks >= 3 and \
