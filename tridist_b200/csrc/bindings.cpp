@@ -1,4 +1,6 @@
-// Python bindings (module `tridist_b200._C`).
+// Python bindings (module `tridist_b200._C`): the native layer under tridist_b200/parallel and
+// tridist_b200/ops, where the reference binds its host library through ctypes
+// (pydushmem/host.py:64-301).
 #include <c10/cuda/CUDAStream.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>

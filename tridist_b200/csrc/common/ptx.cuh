@@ -4,6 +4,11 @@
 //
 // Every wrapper is a single instruction (or the instruction plus the predicate
 // plumbing it needs); policies such as bounded waiting live in sync.cuh.
+//
+// Role in the stack: what the reference gets from its device-side one-sided library (14
+// extern wrappers: put / get / signal / atomics / fence / quiet, pydushmem/device.py:29-168 over
+// pydushmem/src/dushmem_wrapper.cu:8-88) is here a handful of system-scope loads, stores and
+// fences on peer-mapped addresses, plus the Blackwell copy and tensor engines.
 #pragma once
 #include <cstdint>
 #include <cuda.h>

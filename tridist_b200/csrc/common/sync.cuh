@@ -1,5 +1,11 @@
 // Bounded waits and the error-status plane shared by every kernel.
 //
+// The reference waits inside its kernels with an unbounded hybrid spin on monotonic flags (128
+// volatile loads, then one atomic probe: triton_dist/kernels/dcu/all_gather_gemm.py:169-186) or
+// with a one-CTA spin kernel / stream wait value (gemm_ar_rd.py:96-125,:167-180), and diagnoses a
+// wedge from the host (tests/dbg_rs_big.py). Here the wait itself carries the limit and the
+// diagnosis.
+//
 // No kernel in this library spins without a limit. A wait that runs out writes
 // one record {code, rank, site, expected, seen, aux} to the context's status
 // block (first writer wins), raises the context-wide abort word that every

@@ -1,5 +1,11 @@
 // Small sm_100a kernels around the fused operators: SwiGLU, the cross-rank
 // ticket barrier, the bounded-wait self test, and spot verification of a GEMM result.
+//
+// Reference counterparts: the monotonic-round barrier (engine writes of the round number into every
+// rank's slot + a one-CTA spin kernel, triton_dist/kernels/dcu/common_ops.py:212-256), the
+// flag wait kernel (gemm_ar_rd.py:112-125), SwiGLU of the TP-MLP bench
+// (bench/s21_bench_tp_mlp_dcu.py:21-22) and the spot verification of the skew layer
+// (ag_tr_pred.py:533-566).
 #pragma once
 #include <cstdint>
 #include <vector>

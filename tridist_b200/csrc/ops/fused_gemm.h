@@ -1,4 +1,10 @@
 // Plain-C++ interface of the fused GEMM family (no torch / pybind types here).
+//
+// One plan type covers what the reference implements as separate producer / consumer kernels
+// plus host-driven copies per operator: all_gather_gemm.py:98-230 (consumer GEMM gated on arrival
+// flags), gemm_reduce_scatter.py:39-135 (producer GEMM, scatter, consumer reduce),
+// gemm_allreduce.py:73-181 (producer GEMM, push, consumer reduce), all under
+// triton_dist/kernels/dcu/.
 #pragma once
 #include <array>
 #include <cstdint>

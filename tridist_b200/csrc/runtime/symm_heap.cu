@@ -1,3 +1,10 @@
+// Symmetric heap over CUDA IPC and the mapped status block.
+//
+// Counterpart of the reference's symmetric memory (heap malloc/free and ptr(addr, pe) address
+// translation, pydushmem/host.py:239-264) and of its raw IPC pointer list (hipMalloc + IPC handle
+// exchange + open, pydushmem/ipc.py:79-116): one cudaMalloc per rank and buffer, handles exchanged
+// by the host layer, every peer's copy mapped into this process. The handle exchange itself
+// (the reference's MPI allgather, ipc.py:44) is done in Python over torch.distributed.
 #include "symm_heap.h"
 
 #include <cuda_runtime.h>
