@@ -103,6 +103,18 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
 
 static int64_t py_gemm_plan_create(const py::dict& d) { return gemm_plan_create(gemm_desc_from(d)); }
 
+static std::vector<std::string> py_plan_check(const py::dict& d, const py::dict& ext, int sms) {
+  PlanExtents e;
+  e.c_bytes = get<int64_t>(ext, "c_bytes", 0);
+  e.ws_bytes = get<int64_t>(ext, "ws_bytes", 0);
+  e.slot_bytes = get<int64_t>(ext, "slot_bytes", 0);
+  e.res_bytes = get<int64_t>(ext, "res_bytes", 0);
+  e.ag_flag_words = get<int64_t>(ext, "ag_flag_words", 0);
+  e.tile_flag_words = get<int64_t>(ext, "tile_flag_words", 0);
+  e.res_flag_words = get<int64_t>(ext, "res_flag_words", 0);
+  return plan_check(gemm_desc_from(d), e, sms);
+}
+
 static std::vector<std::vector<std::array<int, 5>>> py_schedule_dump(const py::dict& d, int sms) {
   return schedule_dump(gemm_desc_from(d), sms);
 }
@@ -220,6 +232,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     multimem_probe_launch(mc_in, mc_out, local_out, begin, end, blocks, threads, unroll, weak, local_store,
                           cur_stream());
   });
+  m.def("plan_check", &py_plan_check, py::arg("desc"), py::arg("extents"), py::arg("sms") = 148);
   m.def("schedule_dump", &py_schedule_dump, py::arg("desc"), py::arg("sms") = 148);
   m.def("spot_verify", [](int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           bool bf16, int spots, float tol, int64_t bad_tiles, int bn) {

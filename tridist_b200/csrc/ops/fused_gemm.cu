@@ -8,6 +8,7 @@
 #include <array>
 #include <mutex>
 #include <stdexcept>
+#include <vector>
 #include <string>
 #include <unordered_map>
 
@@ -166,6 +167,79 @@ std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d
     }
   }
   return out;
+}
+
+std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e, int sms) {
+  std::vector<std::string> bad;
+  auto need = [&](const char* what, int64_t want, int64_t have, const char* unit) {
+    if (have > 0 && want > have)
+      bad.push_back(std::string(what) + " needs " + std::to_string(want) + " " + unit + ", has " +
+                    std::to_string(have));
+  };
+  if (d.sched == SCHED_LIST) return bad;      // a tile list is checked against the grid by its maker
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int cta_m = choose_cta_m(d);
+  try {
+    fill_schedule_fields(d, cta_m, p);
+  } catch (const std::exception& ex) {
+    bad.push_back(ex.what());
+    return bad;
+  }
+  const bool multi = d.R > 1;
+  // ---- tiles and tickets: every tile once, ticket indices unique and inside the ticket planes ----
+  const int64_t tickets = (d.sched == SCHED_STRIDED)
+      ? static_cast<int64_t>(p.unit_m) * p.cta_m * p.n_tiles
+      : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  const auto sched = schedule_dump(d, sms);
+  std::vector<char> seen(static_cast<size_t>(p.unit_m) * p.cta_m * p.n_tiles, 0);
+  int64_t real_tiles = 0;
+  for (const auto& cta : sched) {
+    for (const auto& t : cta) {
+      const int mt = t[0], nt = t[1], lin = t[2];
+      if (mt < 0 || mt >= p.unit_m * p.cta_m || nt < 0 || nt >= p.n_tiles) {
+        bad.push_back("tile (" + std::to_string(mt) + ", " + std::to_string(nt) + ") outside the tile grid");
+        continue;
+      }
+      if (lin < 0 || lin >= tickets)
+        bad.push_back("ticket index " + std::to_string(lin) + " outside [0, " + std::to_string(tickets) + ")");
+      char& s = seen[static_cast<size_t>(mt) * p.n_tiles + nt];
+      if (s) bad.push_back("tile (" + std::to_string(mt) + ", " + std::to_string(nt) + ") scheduled twice");
+      s = 1;
+      if (mt < p.m_tiles) ++real_tiles;
+    }
+  }
+  if (real_tiles != static_cast<int64_t>(p.m_tiles) * p.n_tiles)
+    bad.push_back("schedule covers " + std::to_string(real_tiles) + " of " +
+                  std::to_string(static_cast<int64_t>(p.m_tiles) * p.n_tiles) + " tiles");
+  // ---- buffers ------------------------------------------------------------------------------
+  const int64_t out_rows = (multi && d.op == OP_RS) ? p.m_per_rank : d.M;
+  const int64_t out_cols = d.N;
+  need("output c", ((out_rows - 1) * d.ldc + out_cols) * 2, e.c_bytes, "bytes");
+  if (multi && d.op == OP_AG) {
+    need("all-gather workspace", static_cast<int64_t>(d.M) * d.K * 2, e.ws_bytes, "bytes");
+    need("all-gather ticket plane", static_cast<int64_t>(d.R) * p.n_chunks, e.ag_flag_words, "words");
+    if (static_cast<int64_t>(p.chunk_rows) * p.n_chunks != p.m_per_rank)
+      bad.push_back("chunk_rows * n_chunks differs from the rows per rank");
+    if (static_cast<int64_t>(p.m_per_rank) * d.R != d.M)
+      bad.push_back("rows per rank * ranks differs from M");
+  }
+  if (multi && (d.op == OP_RS || d.op == OP_AR1 || d.op == OP_AR2)) {
+    const int64_t plane = (d.op == OP_RS ? static_cast<int64_t>(p.m_per_rank) : d.M) * d.N;
+    need(d.nvls ? "local partial plane" : "partial slots",
+         (static_cast<int64_t>(d.R - 1) * d.slot_stride * (d.nvls ? 0 : 1) + plane) * 2, e.slot_bytes, "bytes");
+    if (!d.nvls && d.slot_stride < plane)
+      bad.push_back("slot stride " + std::to_string(d.slot_stride) + " is smaller than one slot (" +
+                    std::to_string(plane) + " elements)");
+    need("tile ticket plane", static_cast<int64_t>(d.R) * tickets, e.tile_flag_words, "words");
+    if (d.op == OP_RS && static_cast<int64_t>(p.m_per_rank) * d.R != d.M)
+      bad.push_back("rows per rank * ranks differs from M");
+  }
+  if (multi && d.op == OP_AR2) {
+    need("result plane", static_cast<int64_t>(d.M) * d.N * 2, e.res_bytes, "bytes");
+    need("result ticket plane", tickets, e.res_flag_words, "words");
+  }
+  return bad;
 }
 
 int64_t gemm_plan_create(const GemmPlanDesc& d) {

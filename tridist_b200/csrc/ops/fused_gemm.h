@@ -9,6 +9,7 @@
 #include <array>
 #include <cstdint>
 #include <cstring>
+#include <string>
 #include <vector>
 
 namespace tdb {
@@ -76,6 +77,22 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
 // needed): for every CTA of the grid the tiles it would process, in order, as
 // {m_tile, n_tile, ticket index, owner key, scheduling position}. `sms` = SMs of the target GPU.
 std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d, int sms);
+
+// Sizes of the buffers a plan will touch (0 = not given, that check is skipped).
+struct PlanExtents {
+  int64_t c_bytes = 0;           // caller's output, from its first element
+  int64_t ws_bytes = 0;          // all-gather workspace, one parity
+  int64_t slot_bytes = 0;        // partial slots (or the local partial plane), one parity
+  int64_t res_bytes = 0;         // all-reduce result plane, one parity
+  int64_t ag_flag_words = 0;     // all-gather chunk tickets
+  int64_t tile_flag_words = 0;   // tile tickets
+  int64_t res_flag_words = 0;    // result tickets
+};
+
+// Trap-free bounds check on the host, before any launch: replays the plan's tile schedule with the
+// functions the kernel uses and checks every ticket index and every buffer offset the kernel will
+// compute against the given extents. Returns one sentence per violation (empty = consistent).
+std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e, int sms);
 
 int64_t launch_count();
 void launch_count_add(int64_t n);

@@ -134,6 +134,24 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
     return d
 
 
+def tensor_extent_bytes(t: torch.Tensor) -> int:
+    """Bytes from the tensor's first element to the end of its storage."""
+    return int(t.untyped_storage().nbytes() - t.storage_offset() * t.element_size())
+
+
+def debug_check(d: Dict, **extents) -> None:
+    """With ``TRIDIST_DEBUG=1``: before a plan is created, replay its tile schedule on the host and
+    check every ticket index and buffer offset the kernel will compute against the sizes of the
+    buffers it is given (a bounds check that cannot fault: nothing is launched). Raises
+    ``TriDistError`` with one sentence per violation."""
+    if not env_int("TRIDIST_DEBUG", 0):
+        return
+    bad = native().plan_check(d, {k: int(v) for k, v in extents.items()}, 148)
+    if bad:
+        from ..parallel.runtime import TriDistError
+        raise TriDistError("plan check failed: " + "; ".join(bad))
+
+
 # ---------------------------------------------------------------------------
 # Plain single-GPU GEMM (the R = 1 degenerate of every fused operator and the
 # building block of the tile-config sweeps)
@@ -191,6 +209,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         if max_ctas:
             d["max_ctas"] = max_ctas
         d["probe"] = probe
+        debug_check(d, c_bytes=tensor_extent_bytes(out))
         return native().gemm_plan_create(d)
 
     pid = _plain_cache.get(key, make)

@@ -30,7 +30,7 @@ from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_wor
                                 native)
 from ..utils.config import env_int
 from ._gemm_common import (BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
-                           base_desc, choose_bn, rotation_order)
+                           base_desc, choose_bn, debug_check, rotation_order, tensor_extent_bytes)
 
 _CONSUMER_BLOCK_M = 128
 _CONSUMER_BLOCK_N = 128
@@ -149,6 +149,10 @@ def _plan(ctx, a, b, c, swiglu=False):
             rounds = units / 74.0
             d["push_ctas"] = env_int("TRIDIST_PUSH_CTAS", 32)
             d["push_skip_rounds"] = env_int("TRIDIST_PUSH_SKIP", 1 if rounds >= 4 else 0)
+            debug_check(d, c_bytes=tensor_extent_bytes(c), ws_bytes=ctx.max_M * K * 2,
+                        ag_flag_words=ctx.flags.nbytes // 4)
+        else:
+            debug_check(d, c_bytes=tensor_extent_bytes(c))
         return native().gemm_plan_create(d)
 
     return ctx.plans.get(key, make)

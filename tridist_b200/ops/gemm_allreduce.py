@@ -45,7 +45,7 @@ from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_wor
                                 native)
 from ..utils.config import env_int, env_str
 from ._gemm_common import (BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_STRIDED, PlanCache,
-                           base_desc, choose_bn, rotation_order)
+                           base_desc, choose_bn, debug_check, rotation_order, tensor_extent_bytes)
 
 
 @dataclass
@@ -216,6 +216,12 @@ def _plan(ctx, a, b, c, mode, parity):
                 d["peer_res"] = [ctx.res.ptrs(0), ctx.res.ptrs(plane)]
             d["peer_res_flags"] = ctx.res_flags.ptrs()
             d["res_is_c"] = res_is_c
+        ext = dict(c_bytes=tensor_extent_bytes(c))
+        if op in (OP_AR1, OP_AR2):
+            ext.update(slot_bytes=plane if mode == "nvls" else R * plane, tile_flag_words=ctx.tile_flags.nbytes // 4)
+        if op == OP_AR2:
+            ext.update(res_bytes=plane, res_flag_words=ctx.res_flags.nbytes // 4)
+        debug_check(d, **ext)
         return native().gemm_plan_create(d)
 
     return ctx.plans.get(key, make)

@@ -29,7 +29,7 @@ from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ._gemm_common import (BM, OP_RS, SCHED_NATURAL, SCHED_SEGMENT, PlanCache, base_desc, choose_bn,
-                           rotation_order)
+                           debug_check, rotation_order, tensor_extent_bytes)
 
 
 @dataclass
@@ -90,6 +90,10 @@ def _plan(ctx, a, b, out):
             d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
             d["slot_stride"] = m_pr * N
             d["peer_tile_flags"] = ctx.tile_flags.ptrs()
+            debug_check(d, c_bytes=tensor_extent_bytes(out), slot_bytes=half,
+                        tile_flag_words=ctx.tile_flags.nbytes // 4)
+        else:
+            debug_check(d, c_bytes=tensor_extent_bytes(out))
         return native().gemm_plan_create(d)
 
     return ctx.plans.get(key, make)

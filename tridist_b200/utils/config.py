@@ -11,6 +11,8 @@ TRIDIST_FORCE_BN          128 or 256: override the output-tile width heuristic
 TRIDIST_CTA_PAIR          0: never run 256-wide tiles on CTA pairs (2-CTA tcgen05 MMA); default 1
 TRIDIST_PUSH_CTAS         CTAs that drive the all-gather push (default 32; 0 = all)
 TRIDIST_PUSH_SKIP         scheduling rounds the pushing CTAs sit out (default 1 on large problems)
+TRIDIST_DEBUG             1: before a plan is created, replay its tile schedule on the host and check every
+                          ticket index and buffer offset against the buffers' sizes (nothing is launched)
 TRIDIST_PROF              1: collect per-CTA stall accounting of the fused GEMM kernels
 TRIDIST_AR_MODE           "auto" | "one_shot" | "two_shot" | "nvls"
 TRIDIST_AR_ONE_SHOT_BYTES size threshold (bytes of one rank's partial) below which
