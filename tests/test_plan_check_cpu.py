@@ -80,3 +80,38 @@ def test_all_reduce(mode):
 
 def test_unknown_extents_are_skipped():
     assert _check(dict(M=1024, N=1024)) == []
+
+
+def test_random_shapes_schedule_is_consistent():
+    """300 pseudo-random (operator, shape, ranks, tile width, pairing, push) combinations: every tile
+    once, ticket indices unique and in range (odd numbers of row blocks with CTA pairs included)."""
+    import random
+    rnd = random.Random(7)
+    checked = 0
+    while checked < 300:
+        R = rnd.choice([1, 2, 4, 8])
+        op = rnd.choice([OP_PLAIN, OP_AG, OP_RS, OP_AR1, OP_AR2]) if R > 1 else OP_PLAIN
+        rank = rnd.randrange(R)
+        if op in (OP_AG, OP_RS):
+            m_pr = rnd.choice([128, 256, 384, 512, 1024, 1152]) if op == OP_AG else rnd.choice([64, 128, 256, 384, 1152])
+            M = m_pr * R
+            if M % 128:
+                continue
+        else:
+            M = rnd.choice([64, 128, 192, 256, 384, 1024, 4096, 4224])
+            m_pr = M
+        N = rnd.choice([128, 256, 384, 768, 1024, 2048, 8192, 6272])
+        d = dict(op=op, bn=rnd.choice([128, 256]), R=R, rank=rank, M=M, N=N, K=1024, allow_pair=rnd.choice([0, 1]))
+        if op == OP_AG:
+            d.update(sched=SCHED_SEGMENT, m_per_rank=m_pr, seg_order=rotation_order(rank, R, 1, own_last=False),
+                     chunk_rows=m_pr, n_chunks=1, push_ctas=rnd.choice([0, 8, 32]), push_skip_rounds=rnd.choice([0, 1, 2]))
+        elif op == OP_RS:
+            d.update(sched=SCHED_SEGMENT if m_pr % 128 == 0 else SCHED_NATURAL, m_per_rank=m_pr,
+                     seg_order=rotation_order(rank, R, 1, own_last=True), slot_stride=m_pr * N)
+        elif op == OP_AR2:
+            d.update(sched=SCHED_STRIDED, seg_order=rotation_order(rank, R, 1, own_last=True),
+                     strided_interleave=rnd.choice([0, 1]), slot_stride=M * N)
+        elif op == OP_AR1:
+            d.update(slot_stride=M * N)
+        assert _check(d) == [], d
+        checked += 1

@@ -193,6 +193,7 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
       : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const auto sched = schedule_dump(d, sms);
   std::vector<char> seen(static_cast<size_t>(p.unit_m) * p.cta_m * p.n_tiles, 0);
+  std::vector<char> ticket_used(static_cast<size_t>(tickets > 0 ? tickets : 1), 0);
   int64_t real_tiles = 0;
   for (const auto& cta : sched) {
     for (const auto& t : cta) {
@@ -201,8 +202,15 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
         bad.push_back("tile (" + std::to_string(mt) + ", " + std::to_string(nt) + ") outside the tile grid");
         continue;
       }
-      if (lin < 0 || lin >= tickets)
+      // the second CTA of the last pair can stand past the last row block (odd number of row
+      // blocks): such a tile has no rows, the kernel touches no ticket for it
+      const bool has_rows = mt < p.m_tiles;
+      if ((has_rows || d.sched == SCHED_STRIDED) && (lin < 0 || lin >= tickets))
         bad.push_back("ticket index " + std::to_string(lin) + " outside [0, " + std::to_string(tickets) + ")");
+      if ((has_rows || d.sched == SCHED_STRIDED) && lin >= 0 && lin < tickets) {
+        if (ticket_used[lin]) bad.push_back("ticket index " + std::to_string(lin) + " used by two tiles");
+        ticket_used[lin] = 1;
+      }
       char& s = seen[static_cast<size_t>(mt) * p.n_tiles + nt];
       if (s) bad.push_back("tile (" + std::to_string(mt) + ", " + std::to_string(nt) + ") scheduled twice");
       s = 1;
