@@ -34,3 +34,19 @@ def test_fallback_wording():
     peaks = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
     md = summarize(read_raw_csv(CSV)[:1], "t", "c", flops=1e11, peaks=peaks)
     assert "of fallback" in md and "of measured" not in md
+
+
+def test_report_tables_from_recorded_lines(tmp_path):
+    import json
+    from bench.report import load, tables
+    runs = {}
+    for n, ms in ((1, 32.0), (8, 8.0)):
+        line = {"n_gpus": n, "ms_per_step": ms, "e2e": {"value": 2 * ms}, "clocks": {"sm_mhz": 1400.0, "reasons": []},
+                "ops": {"ag_gemm": {"fused_p50_ms": ms / 8, "cublas_nccl_p50_ms": ms / 7, "speedup_vs_cublas_nccl": 8 / 7,
+                                    "roofline_frac": 0.7}}}
+        p = tmp_path / f"b{n}.json"
+        p.write_text("log line\n" + json.dumps(line) + "\n")          # a log with the JSON line last also loads
+        runs[n] = str(p)
+    md = tables(load(list(runs.values())))
+    assert "| ag_gemm | 4.000 / 4.571 (1.14) | 1.000 / 1.143 (1.14) | 0.7 |" in md
+    assert "| 8 | 8.000 | 16.0 | 0.50 | 1400.0 | - |" in md           # 32 ms on 1 GPU -> 8 ms on 8: efficiency 0.5
