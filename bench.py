@@ -137,6 +137,9 @@ def main() -> None:
         roof = w.roof()
         ops[w.name] = {"in_step_p50_ms": round(p50, 4), "roofline_ms": round(roof["ms"], 4),
                        "check_max_abs_err": errs[w.name]}
+        algo = getattr(w, "algorithm", None)
+        if algo is not None:
+            ops[w.name]["algorithm"] = algo() if callable(algo) else algo
 
     # ---- per-operator p50: fused and cuBLAS+NCCL in the SAME harness -------------------------
     # (L2 flush, then a device-side barrier of all ranks, then one event pair around the call)

@@ -152,6 +152,11 @@ class GemmAR(Workload):
     def digest(self):
         return self.c[0, :8].float().sum()
 
+    def algorithm(self):
+        """Which all-reduce form the context picks for this shape (one_shot / two_shot / nvls / local)."""
+        from tridist_b200.ops.gemm_allreduce import pick_mode
+        return pick_mode(self.ctx, self.M)
+
     def roof(self):
         from tridist_b200.ops.gemm_allreduce import pick_mode
         two = pick_mode(self.ctx, self.M) in ("two_shot", "nvls")
