@@ -209,6 +209,8 @@ def main() -> None:
         }
         if e2e is not None:
             out["e2e"] = e2e
+        if getattr(rt, "multicast_unavailable", None):
+            out["multicast_unavailable"] = str(rt.multicast_unavailable)
         print(json.dumps(out))
     sync_all()
     if world > 1:
