@@ -13,6 +13,12 @@ def _delegate(name):
     return f
 
 
-for _n in ("malloc", "calloc", "free", "ptr", "putmem", "putmem_nbi", "getmem", "getmem_nbi", "quiet", "fence",
-           "barrier_all", "my_pe", "n_pes"):
+for _n in ("malloc", "calloc", "align", "free", "ptr", "putmem", "putmem_nbi", "getmem", "getmem_nbi", "quiet",
+           "fence", "barrier_all", "my_pe", "n_pes", "finalize"):
     globals()[_n] = _delegate(_n)
+
+
+def get_uniqueid() -> bytes:
+    """The reference exchanges a library unique id before ``init`` (pydushmem/__init__.py:22-35); the
+    rendezvous here is torch.distributed's, so the id carries no information."""
+    return b"tridist_b200"

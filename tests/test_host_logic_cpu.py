@@ -63,5 +63,7 @@ def test_reference_import_paths():
     assert moe_a2a.moe_dispatch_intra_node_op is ops.moe_dispatch_intra_node_op
     assert i1_predictor.StickyOrderPredictor is ops.StickyOrderPredictor
     assert pydushmem.host.mpi_comm_size() >= 1
-    for name in ("malloc", "ptr", "putmem", "getmem", "barrier_all", "my_pe", "n_pes"):
+    assert pydushmem.get_uniqueid()
+    for name in ("malloc", "calloc", "align", "free", "ptr", "putmem", "putmem_nbi", "getmem", "getmem_nbi", "quiet",
+                 "fence", "barrier_all", "my_pe", "n_pes", "finalize"):
         assert callable(getattr(pydushmem, name))

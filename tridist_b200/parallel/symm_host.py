@@ -39,8 +39,22 @@ class SymmHost:
 
     calloc = malloc
 
+    def align(self, alignment: int, nbytes: int) -> SymmBuffer:
+        """Collective; every symmetric buffer starts on a 256-byte boundary (the reference's
+        ``dushmem_align``, pydushmem/host.py:239-249)."""
+        if alignment <= 0 or alignment & (alignment - 1) or alignment > 256:
+            raise ValueError("alignment must be a power of two up to 256 bytes")
+        return self.malloc(nbytes)
+
     def free(self, buf: SymmBuffer) -> None:
         self.world.free(buf)
+
+    def finalize(self) -> None:
+        """Collective: release every symmetric buffer and the process-wide world."""
+        global _host
+        from .runtime import finalize_runtime
+        finalize_runtime()
+        _host = None
 
     def ptr(self, buf: SymmBuffer, pe: int, byte_offset: int = 0) -> int:
         """Address of ``pe``'s copy, valid in this process (the reference's ``dushmem_ptr``)."""
