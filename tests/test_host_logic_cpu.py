@@ -67,3 +67,5 @@ def test_reference_import_paths():
     for name in ("malloc", "calloc", "align", "free", "ptr", "putmem", "putmem_nbi", "getmem", "getmem_nbi", "quiet",
                  "fence", "barrier_all", "my_pe", "n_pes", "finalize"):
         assert callable(getattr(pydushmem, name))
+        from tridist_b200.parallel.symm_host import SymmHost
+        assert hasattr(SymmHost, name), name          # the delegate names a real method
