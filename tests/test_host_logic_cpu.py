@@ -62,6 +62,10 @@ def test_reference_import_paths():
     assert gemm_allreduce.gemm_ar_intra_node is ops.gemm_ar_intra_node
     assert moe_a2a.moe_dispatch_intra_node_op is ops.moe_dispatch_intra_node_op
     assert i1_predictor.StickyOrderPredictor is ops.StickyOrderPredictor
+    from triton_dist.kernels.dcu import common_ops
+    for name in ("init_dcu", "dcu_state", "memcpy_async", "fan_out_memcpy_async", "set_signal", "wait_eq",
+                 "SymmBarrier", "barrier_all_on_stream"):
+        assert callable(getattr(common_ops, name)), name
     assert pydushmem.host.mpi_comm_size() >= 1
     assert pydushmem.get_uniqueid()
     for name in ("malloc", "calloc", "align", "free", "ptr", "putmem", "putmem_nbi", "getmem", "getmem_nbi", "quiet",
