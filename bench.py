@@ -144,7 +144,7 @@ def main() -> None:
     # ---- per-operator p50: fused and cuBLAS+NCCL in the SAME harness -------------------------
     # (L2 flush, then a device-side barrier of all ranks, then one event pair around the call)
     for w in wls:
-        r = time_op(w.run, iters=args.steps, warmup=2, flush=True, barrier=rt.barrier_on_stream)
+        r = time_op(w.run, iters=args.steps, warmup=3, flush=True, barrier=rt.barrier_on_stream)
         o = ops[w.name]
         o["fused_p50_ms"] = round(r["p50"], 4)
         o["fused_min_ms"] = round(r["min"], 4)
