@@ -74,9 +74,89 @@ def _all_ops(rank, R):
     w.host_barrier()
 
 
-def test_all_ops_two_gpus():
+def _n_gpus() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _need(n):
+    return pytest.mark.skipif(_n_gpus() < n, reason=f"needs >= {n} CUDA devices")
+
+
+@pytest.mark.parametrize("R", [2, pytest.param(4, marks=_need(4)), pytest.param(8, marks=_need(8))])
+def test_all_ops(R):
     from tridist_b200.utils.testing import spawn
-    spawn(_all_ops, 2, backend="nccl", timeout=600)
+    spawn(_all_ops, R, backend="nccl", timeout=600)
+
+
+def _alternating_m(rank, R):
+    """One context, calls that alternate between its largest M and smaller ones, with one rank
+    held back on the host before every call: a ticket word must keep its (source, index) meaning
+    across shapes, or a rank that runs a round ahead raises a word another source still owns."""
+    import time
+    from tridist_b200.models.tp_mlp import TPMLP, TPMLPConfig, reference_forward
+    from tridist_b200.ops import (ag_gemm_intra_node_op, create_ag_gemm_intra_node_context,
+                                  create_gemm_ar_intra_node_context, create_gemm_rs_intra_node_context,
+                                  gemm_ar_intra_node_op, gemm_rs_intra_node)
+    from tridist_b200.parallel.runtime import init_runtime
+    from tridist_b200.utils.testing import ag_inputs, ks_inputs
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    w = init_runtime(rank, R)
+    dt = torch.float16
+    max_M, N, kl, K = 256 * R * 2, 512, 256, 512
+    sizes = [max_M, max_M // 2, max_M, max_M // 4, max_M // 2, max_M]
+    rs = create_gemm_rs_intra_node_context(max_M, N, dt, rank, R)
+    ar = create_gemm_ar_intra_node_context(max_M, N, dt, dt, rank, R, nvls=False)
+    ag = create_ag_gemm_intra_node_context(max_M, K, dt, dt, rank, R, M_PER_CHUNK=128)
+    for it, M in enumerate(sizes):
+        if rank == (it % R):
+            time.sleep(0.02)                     # this rank enters the round late
+        a_all, b_all = ks_inputs(R, M, N, kl, 100 + it, dt)
+        ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
+        a, b = a_all[rank].cuda(), b_all[rank].cuda()
+        out = gemm_rs_intra_node(a, b, rs)
+        mp_ = M // R
+        for mode in ("one_shot", "two_shot"):
+            ar.mode = mode
+            c = torch.empty(M, N, dtype=dt, device="cuda")
+            gemm_ar_intra_node_op(a, b, c, ar)
+            torch.cuda.synchronize()
+            w.check()
+            assert (c.float() - ref).abs().max().item() < TOL, f"AR {mode} round {it} M={M}"
+        assert (out.float() - ref[rank * mp_:(rank + 1) * mp_]).abs().max().item() < TOL, f"RS round {it} M={M}"
+        a_sh, bw = ag_inputs(rank, R, M // R, K, N, 200 + it, dt)
+        cg = torch.empty(M, N, dtype=dt, device="cuda")
+        ag_gemm_intra_node_op(a_sh[rank].cuda(), bw.cuda(), cg, ag)
+        torch.cuda.synchronize()
+        w.check()
+        refg = torch.cat(a_sh, 0).cuda().float() @ bw.cuda().float().t()
+        assert (cg.float() - refg).abs().max().item() < TOL, f"AG round {it} M={M}"
+    # the TP-MLP layer slices its contexts to the token count of each call
+    dtb = torch.bfloat16
+    hid, inter = 512, 256 * R
+    g = torch.Generator().manual_seed(5)
+    w_gu = [(torch.randn(2 * inter // R, hid, generator=g) * 0.05).to(dtb) for _ in range(R)]
+    w_dn = [(torch.randn(hid, inter // R, generator=g) * 0.05).to(dtb) for _ in range(R)]
+    layer = TPMLP(TPMLPConfig(hidden=hid, intermediate=inter, max_tokens=max_M, dtype=dtb), rank, R,
+                  w_gu[rank].cuda(), w_dn[rank].cuda())
+    for it, M in enumerate(sizes):
+        if rank == ((it + 1) % R):
+            time.sleep(0.02)
+        xs = [(torch.randn(M // R, hid, generator=torch.Generator().manual_seed(300 + it * 16 + s))).to(dtb)
+              for s in range(R)]
+        y = layer(xs[rank].cuda())
+        torch.cuda.synchronize()
+        w.check()
+        ref = reference_forward(torch.cat(xs, 0).cuda(), [t.cuda() for t in w_gu], [t.cuda() for t in w_dn])
+        mp_ = M // R
+        err = (y.float() - ref[rank * mp_:(rank + 1) * mp_]).abs().max().item()
+        assert err < 5e-2, f"TP-MLP round {it} M={M}: {err}"
+    w.host_barrier()
+
+
+@pytest.mark.parametrize("R", [2, pytest.param(4, marks=_need(4))])
+def test_alternating_m_on_one_context(R):
+    from tridist_b200.utils.testing import spawn
+    spawn(_alternating_m, R, backend="nccl", timeout=600)
 
 
 def _nvls_all_reduce(rank, R):
@@ -135,6 +215,7 @@ def _nvls_all_reduce(rank, R):
     assert not problems, problems
 
 
-def test_nvls_all_reduce_two_gpus():
+@pytest.mark.parametrize("R", [2, pytest.param(4, marks=_need(4)), pytest.param(8, marks=_need(8))])
+def test_nvls_all_reduce(R):
     from tridist_b200.utils.testing import spawn
-    spawn(_nvls_all_reduce, 2, backend="nccl", timeout=300)
+    spawn(_nvls_all_reduce, R, backend="nccl", timeout=300)

@@ -69,13 +69,18 @@ def test_all_reduce(mode):
         d.update(nvls=1, slot_stride=0, mc_part=[1 << 40, (1 << 40) + 2 * plane], mc_res=[1 << 41, (1 << 41) + 2 * plane])
     good = dict(c_bytes=plane * 2, slot_bytes=(plane if mode == "nvls" else R * plane) * 2, tile_flag_words=R * tickets)
     if mode != "one_shot":
-        good.update(res_bytes=plane * 2, res_flag_words=tickets)
+        good.update(res_bytes=plane * 2, res_flag_words=R * tickets)      # result tickets: one row per owner
     assert _check(d, **good) == []
     assert _check(d, **dict(good, slot_bytes=good["slot_bytes"] - 2)) != []
     assert _check(d, **dict(good, tile_flag_words=R * tickets - 1)) != []
     if mode != "one_shot":
         assert any("result plane" in s for s in _check(d, **dict(good, res_bytes=plane * 2 - 2)))
-        assert any("result ticket plane" in s for s in _check(d, **dict(good, res_flag_words=tickets - 1)))
+        assert any("result ticket plane" in s for s in _check(d, **dict(good, res_flag_words=R * tickets - 1)))
+        # a context-wide stride larger than this call's ticket count widens both planes
+        wide = dict(d, ticket_stride=2 * tickets)
+        assert _check(wide, **good) != []
+        assert _check(wide, **dict(good, tile_flag_words=(R - 1) * 2 * tickets + tickets,
+                                   res_flag_words=(R - 1) * 2 * tickets + tickets)) == []
 
 
 def test_unknown_extents_are_skipped():

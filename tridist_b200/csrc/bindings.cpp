@@ -80,6 +80,8 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   fill_ptrs2(d, "peer_slots", g.peer_slots);
   fill_ptrs(d, "peer_tile_flags", g.peer_tile_flags, 8);
   g.slot_stride = get<int64_t>(d, "slot_stride", 0);
+  g.ticket_stride = get<int>(d, "ticket_stride", 0);
+  g.ag_flag_stride = get<int>(d, "ag_flag_stride", 0);
   fill_ptrs2(d, "peer_res", g.peer_res);
   fill_ptrs(d, "peer_res_flags", g.peer_res_flags, 8);
   g.res_is_c = get<int>(d, "res_is_c", 0);

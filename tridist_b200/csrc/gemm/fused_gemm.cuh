@@ -158,7 +158,7 @@ struct alignas(64) GemmParams {
   uint32_t* peer_tile_flags[kMaxRanks];  // [R][tiles] tickets on every rank, indexed by source
   int64_t slot_stride;             // elements between two sources' slots
   void* peer_res[kMaxRanks];       // OP_AR2: reduced-result buffer [M][N] on every rank
-  uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [tiles] tickets
+  uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [R][ticket_stride] tickets, indexed by owner
   int32_t res_is_c;                // OP_AR2: caller's c aliases peer_res[rank]; skip the copy
   // OP_AR2 through the switch: partials stay in this rank's own buffer (peer_slots[*] all name
   // it, slot_stride = 0); the owner of a tile sums the R copies with multimem.ld_reduce on
@@ -176,6 +176,11 @@ struct alignas(64) GemmParams {
   // ring is filled once and every k-block re-multiplies resident stages without waiting for
   // loads; 2 = operand-feed ceiling, every stage is loaded and released without any MMA.
   int32_t probe;
+  // Words between two sources' rows of the ticket planes. They are properties of the context
+  // (its largest shape), not of the call: a word then belongs to one (source, index) pair for
+  // the whole life of the context, whatever M the calls use.
+  int32_t ticket_stride;   // tile tickets: [source][ticket_stride]
+  int32_t ag_flag_stride;  // all-gather chunk tickets: [source][ag_flag_stride]
   int32_t pad_;
 };
 
@@ -527,7 +532,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               const int r_hi = min(r_lo + BM, p.m_per_rank) - 1;
               for (int ck = r_lo / p.chunk_rows; ok && ck <= r_hi / p.chunk_rows; ++ck) {
                 if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
-                const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.n_chunks + ck;
+                const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.ag_flag_stride + ck;
                 const uint64_t tw = prof ? globaltimer_ns() : 0;
                 ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck);
                 if (prof) acc_a += globaltimer_ns() - tw;
@@ -708,7 +713,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int etid = (warp - kEpiWarp0) * 32 + lane;
     const int64_t ldc = p.ldc;
-    const int tiles = p.unit_m * p.cta_m * p.n_tiles;   // ticket words per source
+    const int tiles = p.ticket_stride;                  // ticket words per source
     const bool multi = p.R > 1;
     uint64_t acc_busy = 0, acc_pub = 0, acc_tick = 0, n_tiles_done = 0;
     int it = 0;
@@ -1037,7 +1042,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           if (old + 1u == static_cast<uint32_t>(p.push_parts)) {
             atomicExch(cnt, 0u);
             fence_acq_rel_sys();
-            st_release_sys(p.peer_ag_flags[dest] + p.rank * p.n_chunks + ck, p.round);
+            st_release_sys(p.peer_ag_flags[dest] + p.rank * p.ag_flag_stride + ck, p.round);
           }
         }
       }
@@ -1064,7 +1069,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           if (ctid == 0) s_flags[1] = 1;
           named_bar_sync(1, kCommThreads);
           if (ctid < p.R &&
-              !wait_flag_ge(p.peer_tile_flags[p.rank] + ctid * tickets + lin, p.round, env, SITE_AR_TILE,
+              !wait_flag_ge(p.peer_tile_flags[p.rank] + ctid * p.ticket_stride + lin, p.round, env, SITE_AR_TILE,
                             (ctid << 24) | lin))
             s_flags[1] = 0;
           named_bar_sync(1, kCommThreads);     // also orders the slot reads after the acquires
@@ -1171,7 +1176,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           // the releases below (one warp) are cumulative over the stores this barrier orders
           named_bar_sync(1, kCommThreads);
           if (cprof) prof[PROF_TL_OWN_FENCED] = globaltimer_ns() - t_kernel0;
-          if (ctid < p.R && ctid != p.rank) st_release_sys(p.peer_res_flags[ctid] + lin, p.round);
+          // the owner's row of the plane: one writer per word, whatever the shapes of earlier calls
+          if (ctid < p.R && ctid != p.rank)
+            st_release_sys(p.peer_res_flags[ctid] + p.rank * p.ticket_stride + lin, p.round);
           if (cprof) {
             prof[PROF_TL_OWN_FLAGGED] = globaltimer_ns() - t_kernel0;
             acc_aw += ta1 - ta0;
@@ -1194,7 +1201,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (mt * BM >= p.M) continue;         // nothing is ever published for an empty row block
         const uint64_t tb0 = cprof ? globaltimer_ns() : 0;
         if (ctid == 0)
-          ok = wait_flag_ge(p.peer_res_flags[p.rank] + lin, p.round, env, SITE_AR_RESULT, lin);
+          ok = wait_flag_ge(p.peer_res_flags[p.rank] + (unit % p.R) * p.ticket_stride + lin, p.round, env,
+                            SITE_AR_RESULT, lin);
         // all comm threads learn the outcome; also orders their loads after the acquire
         if (ctid == 0) s_flags[1] = ok ? 1 : 0;
         named_bar_sync(1, kCommThreads);

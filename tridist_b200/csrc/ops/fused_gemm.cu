@@ -135,6 +135,14 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p
   p.skip_comm = d.skip_comm;
   p.push_ctas = d.push_ctas;
   p.push_skip_rounds = d.push_skip_rounds;
+  const int own_tickets = p.unit_m * p.cta_m * p.n_tiles;
+  if (d.ticket_stride > 0 && d.ticket_stride < own_tickets)
+    throw std::runtime_error("tridist_b200: ticket stride " + std::to_string(d.ticket_stride) +
+                             " is smaller than this call's " + std::to_string(own_tickets) + " tile tickets");
+  if (d.ag_flag_stride > 0 && d.ag_flag_stride < p.n_chunks)
+    throw std::runtime_error("tridist_b200: chunk-ticket stride is smaller than this call's chunk count");
+  p.ticket_stride = d.ticket_stride > 0 ? d.ticket_stride : own_tickets;
+  p.ag_flag_stride = d.ag_flag_stride > 0 ? d.ag_flag_stride : p.n_chunks;
 }
 
 // Persistent grid: one CTA (or CTA pair) per scheduling position, at most one per SM.
@@ -226,7 +234,8 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
   need("output c", ((out_rows - 1) * d.ldc + out_cols) * 2, e.c_bytes, "bytes");
   if (multi && d.op == OP_AG) {
     need("all-gather workspace", static_cast<int64_t>(d.M) * d.K * 2, e.ws_bytes, "bytes");
-    need("all-gather ticket plane", static_cast<int64_t>(d.R) * p.n_chunks, e.ag_flag_words, "words");
+    need("all-gather ticket plane", static_cast<int64_t>(d.R - 1) * p.ag_flag_stride + p.n_chunks,
+         e.ag_flag_words, "words");
     if (static_cast<int64_t>(p.chunk_rows) * p.n_chunks != p.m_per_rank)
       bad.push_back("chunk_rows * n_chunks differs from the rows per rank");
     if (static_cast<int64_t>(p.m_per_rank) * d.R != d.M)
@@ -239,13 +248,15 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
     if (!d.nvls && d.slot_stride < plane)
       bad.push_back("slot stride " + std::to_string(d.slot_stride) + " is smaller than one slot (" +
                     std::to_string(plane) + " elements)");
-    need("tile ticket plane", static_cast<int64_t>(d.R) * tickets, e.tile_flag_words, "words");
+    need("tile ticket plane", static_cast<int64_t>(d.R - 1) * p.ticket_stride + tickets, e.tile_flag_words,
+         "words");
     if (d.op == OP_RS && static_cast<int64_t>(p.m_per_rank) * d.R != d.M)
       bad.push_back("rows per rank * ranks differs from M");
   }
   if (multi && d.op == OP_AR2) {
     need("result plane", static_cast<int64_t>(d.M) * d.N * 2, e.res_bytes, "bytes");
-    need("result ticket plane", tickets, e.res_flag_words, "words");
+    need("result ticket plane", static_cast<int64_t>(d.R - 1) * p.ticket_stride + tickets, e.res_flag_words,
+         "words");
   }
   return bad;
 }

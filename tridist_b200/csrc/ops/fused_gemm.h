@@ -46,6 +46,11 @@ struct GemmPlanDesc {
   int64_t peer_slots[2][8] = {};
   int64_t peer_tile_flags[8] = {};
   int64_t slot_stride = 0;
+  // Words between two sources' rows of the ticket planes (0 = this call's own tile / chunk
+  // count). A context passes the counts of its LARGEST shape, so that a ticket word keeps one
+  // (source, index) meaning for every M the context is called with.
+  int ticket_stride = 0;
+  int ag_flag_stride = 0;
   int64_t peer_res[2][8] = {};
   int64_t peer_res_flags[8] = {};
   int res_is_c = 0;

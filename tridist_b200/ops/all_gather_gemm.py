@@ -119,8 +119,9 @@ def _plan(ctx, a, b, c, swiglu=False):
     order = ctx.order_override or rotation_order(rank, R, 1, own_last=False)
     # emulated launches cannot take a per-call table: a device order table is baked into the plan
     baked_table = getattr(ctx, "emu_order_table", None)
-    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, c.stride(0), a.dtype, swiglu, bn,
-           tuple(order), baked_table.data_ptr() if baked_table is not None else 0, ctx.observe)
+    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, K, a.stride(0), b.stride(0), c.stride(0),
+           a.dtype, swiglu, bn, tuple(order), baked_table.data_ptr() if baked_table is not None else 0,
+           ctx.observe)
 
     def make():
         d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, OP_AG)
@@ -137,6 +138,7 @@ def _plan(ctx, a, b, c, swiglu=False):
             half = ctx.max_M * K * 2
             d["peer_ws"] = [ctx.ws.ptrs(0), ctx.ws.ptrs(half)]
             d["peer_ag_flags"] = ctx.flags.ptrs()
+            d["ag_flag_stride"] = ctx.max_chunks     # one word per (source, chunk) for every M
             d["ag_counters"] = ctx.counters.data_ptr()
             d["arrival_ns"] = ctx.arrival_ns.data_ptr() if ctx.observe else 0
             chunk = min(ctx.M_PER_CHUNK, m_pr)

@@ -61,7 +61,7 @@ class GemmARContext:
     slots: Optional[SymmBuffer] = None       # [2][R, max_M, N] partials by source
     res: Optional[SymmBuffer] = None         # [2][max_M, N] reduced result (two-shot)
     tile_flags: Optional[SymmBuffer] = None  # u32 [R, max_tiles]
-    res_flags: Optional[SymmBuffer] = None   # u32 [max_tiles]
+    res_flags: Optional[SymmBuffer] = None   # u32 [R, max_tiles], by owner
     mc: Optional[object] = None              # McBuffer [part 0 | part 1 | res 0 | res 1], each max_M * N
     flag_round: int = 0
     plans: PlanCache = field(default_factory=PlanCache)
@@ -103,7 +103,7 @@ def create_gemm_ar_intra_node_context(max_M, N, input_dtype, output_dtype, rank,
         ctx.slots = world.alloc(2 * num_ranks * max_M * N * 2, rank)
         ctx.res = world.alloc(2 * max_M * N * 2, rank)
         ctx.tile_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)
-        ctx.res_flags = world.alloc(ctx.max_tiles * 4, rank)
+        ctx.res_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)
         if nvls is None:
             nvls = ctx.mode == "nvls" or (ctx.mode == "auto" and num_ranks >= 3)
         if nvls:
@@ -198,6 +198,7 @@ def _plan(ctx, a, b, c, mode, parity):
             d["nvls"] = 1
             d["peer_slots"] = [[ctx.mc.local_ptr] * R, [ctx.mc.local_ptr + plane] * R]
             d["slot_stride"] = 0
+            d["ticket_stride"] = ctx.max_tiles
             d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + plane]
             d["mc_res"] = [ctx.mc.mc_ptr + 2 * plane, ctx.mc.mc_ptr + 3 * plane]
             d["peer_tile_flags"] = ctx.tile_flags.ptrs()
@@ -206,6 +207,7 @@ def _plan(ctx, a, b, c, mode, parity):
             d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
             d["slot_stride"] = M * N
             d["peer_tile_flags"] = ctx.tile_flags.ptrs()
+            d["ticket_stride"] = ctx.max_tiles       # one word per (source, tile) for every M
         if op == OP_AR2:
             d["sched"] = SCHED_STRIDED
             d["seg_order"] = rotation_order(rank, R, 1, own_last=True)

@@ -77,8 +77,8 @@ def _plan(ctx, a, b, out):
     m_pr = M // R
     bn = choose_bn(M, N)
     order = ctx.order_override or rotation_order(rank, R, 1, own_last=True)
-    key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), a.dtype, bn,
-           tuple(order))
+    key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+           a.dtype, bn, tuple(order))
 
     def make():
         d = base_desc(ctx.world, rank, R, a, b, out.data_ptr(), out.stride(0), M, N, K, bn, OP_RS)
@@ -90,6 +90,7 @@ def _plan(ctx, a, b, out):
             d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
             d["slot_stride"] = m_pr * N
             d["peer_tile_flags"] = ctx.tile_flags.ptrs()
+            d["ticket_stride"] = ctx.max_tiles       # one word per (source, tile) for every M
             debug_check(d, c_bytes=tensor_extent_bytes(out), slot_bytes=half,
                         tile_flag_words=ctx.tile_flags.nbytes // 4)
         else:
