@@ -36,10 +36,54 @@ def test_plain_covers_every_tile_once(M, N, bn, pair):
 
 
 def test_pairs_take_adjacent_row_blocks():
-    out = _dump(M=8192, N=6144, bn=256)
+    out = _dump(M=8192, N=6144, bn=256, allow_wide=0)
     for even, odd in zip(out[0::2], out[1::2]):
         assert [(t[0] + 1, t[1]) for t in even] == [(t[0], t[1]) for t in odd]
         assert all(t[0] % 2 == 0 for t in even)
+
+
+def test_wide_pairs_take_four_adjacent_row_blocks():
+    """512 x 256 tiles per CTA pair: each CTA owns two consecutive 128-row blocks, the second
+    CTA of the pair the two that follow."""
+    out = _dump(M=8192, N=6144, bn=256)
+    for even, odd in zip(out[0::2], out[1::2]):
+        assert len(even) % 2 == 0 and len(even) == len(odd)
+        for a, b in zip(even[0::2], even[1::2]):
+            assert a[0] % 4 == 0 and (b[0], b[1]) == (a[0] + 1, a[1])
+        assert [(t[0] + 2, t[1]) for t in even] == [(t[0], t[1]) for t in odd]
+
+
+@pytest.mark.parametrize("M,N,K,bn,pair", [(8192, 6144, 12288, 256, 1), (128, 8192, 3584, 256, 1),
+                                           (128, 8192, 28672, 128, 1), (4096, 8192, 3584, 256, 1),
+                                           (1024, 8192, 3584, 128, 1), (8192, 6144, 12288, 256, 0)])
+def test_remainder_round_is_cut_along_k(M, N, K, bn, pair):
+    """The tiles of the last, partial round are cut into K ranges on consecutive workers: the
+    ranges of a tile partition its k-blocks, slice 0 is the worker that also appears in the tile
+    schedule, and no worker takes more than one slice."""
+    from tridist_b200.parallel.runtime import native
+    d = dict(op=OP_PLAIN, sched=SCHED_NATURAL, bn=bn, R=1, rank=0, M=M, N=N, K=K, allow_pair=pair)
+    cuts = native().splitk_dump(d, 148)
+    out = _dump(M=M, N=N, K=K, bn=bn, allow_pair=pair)
+    seen = [(t[0], t[1]) for cta in out for t in cta if t[0] * BM < M]
+    assert len(seen) == len(set(seen)) and set(seen) == _tiles(M, N, bn)
+    assert cuts, "these shapes leave a partial round"
+    k_blocks = (K + 63) // 64
+    by_pos = {}
+    for pos, cta0, sl, n, kb0, kb1 in cuts:
+        by_pos.setdefault(pos, []).append((sl, n, kb0, kb1, cta0))
+    workers = [c[1] for c in cuts]
+    assert len(workers) == len(set(workers))
+    finisher_pos = {t[4]: c for c, cta in enumerate(out) for t in cta}
+    for pos, parts in by_pos.items():
+        parts.sort()
+        n = parts[0][1]
+        assert [q[0] for q in parts] == list(range(n)) and 2 <= n <= 8
+        assert parts[0][2] == 0 and parts[-1][3] == k_blocks
+        assert all(a[3] == b[2] for a, b in zip(parts, parts[1:]))
+        assert all(q[3] - q[2] >= 8 for q in parts)
+        step = parts[1][4] - parts[0][4]
+        assert [q[4] for q in parts] == [parts[0][4] + i * step for i in range(n)]
+        assert finisher_pos[pos] // step * step == parts[0][4]
 
 
 @pytest.mark.parametrize("R", [2, 4, 8])
@@ -75,7 +119,7 @@ def test_two_shot_owners(R, interleave):
     owned = [0] * R
     for t in tiles:
         owned[t[3] % R] += 1
-    assert max(owned) - min(owned) <= 2          # CTA tiles (two per pair unit) spread evenly over the owners
+    assert max(owned) - min(owned) <= 4          # 128-row blocks (four per pair unit) spread evenly over the owners
     if not interleave:                            # own tiles come last on every worker
         for cta in out:
             own = [t[3] % R == rank for t in cta]

@@ -67,6 +67,9 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);
   g.max_ctas = get<int>(d, "max_ctas", 0);
   g.allow_pair = get<int>(d, "allow_pair", 1);
+  g.allow_wide = get<int>(d, "allow_wide", 1);
+  g.allow_splitk = get<int>(d, "allow_splitk", 1);
+  g.raster_g = get<int>(d, "raster_g", 0);
   fill_ptrs2(d, "peer_ws", g.peer_ws);
   fill_ptrs(d, "peer_ag_flags", g.peer_ag_flags, 8);
   g.ag_counters = get<int64_t>(d, "ag_counters", 0);
@@ -236,6 +239,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("plan_check", &py_plan_check, py::arg("desc"), py::arg("extents"), py::arg("sms") = 148);
   m.def("schedule_dump", &py_schedule_dump, py::arg("desc"), py::arg("sms") = 148);
+  m.def("splitk_dump", [](const py::dict& d, int sms) { return splitk_dump(gemm_desc_from(d), sms); },
+        py::arg("desc"), py::arg("sms") = 148);
   m.def("spot_verify", [](int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           bool bf16, int spots, float tol, int64_t bad_tiles, int bn) {
     spot_verify_launch(a, b, c, M, N, K, lda, ldb, ldc, bf16, spots, tol, bad_tiles, bn, cur_stream());

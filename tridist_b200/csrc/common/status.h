@@ -22,6 +22,7 @@ enum WaitSite : uint32_t {
   SITE_MOE_META = 6,
   SITE_MOE_DISPATCH_DONE = 7,
   SITE_MOE_COMBINE_READY = 8,
+  SITE_SPLITK = 9,         // split-K finisher waiting for another slice's partial
   SITE_PIPE_FULL = 16,
   SITE_PIPE_EMPTY = 17,
   SITE_TMEM_FULL = 18,

@@ -16,10 +16,25 @@
 //              communication warps reduce it and broadcast the result to all ranks
 //
 // Roles inside one CTA (320 threads, one CTA per SM):
-//   warp 0      TMA producer (one lane): smem ring of kStages {A 128x64, B BNx64} tiles
+//   warp 0      TMA producer (one lane): smem ring of kStages {A (kMT x 128) x 64, B x 64} tiles
 //   warp 1      tcgen05.mma issuer (one lane), owns the TMEM allocation (2 accumulators)
-//   warps 2-5   epilogue: tcgen05.ld -> convert -> global / peer stores (+ in-epilogue reduce)
+//   warps 2-5   epilogue: tcgen05.ld -> convert -> staged TMA stores / peer stores (+ in-epilogue reduce)
 //   warps 6-9   communication warps (AG push; AR2 reduce + broadcast + result collection)
+//
+// Tile shapes (template parameters kCtaM = CTAs per MMA, kMT = 128-row blocks per CTA):
+//   kCtaM 1, kMT 1   128 x BN per CTA; the two TMEM accumulators double-buffer whole tiles
+//   kCtaM 2, kMT 1   256 x 256 per CTA pair (cta_group::2), same double buffering
+//   kCtaM 2, kMT 2   512 x 256 per CTA pair: every CTA holds 256 rows of A and its half of B per
+//                    stage and issues two MMAs per K step, one per 128-row half, into the two
+//                    accumulators. Three quarters of the operand bytes per FLOP of the 256 x 256
+//                    pair tile (and of its shared-memory write traffic); the accumulators are no
+//                    longer spare, so the epilogue drains half 0 first and the next tile's half-0
+//                    MMAs start under the drain of half 1.
+//
+// Whole tiles are dealt round-robin to the workers (a worker = a CTA or a CTA pair). The tiles of
+// the last, partial round are cut along K into `sk_slices` ranges, one per otherwise idle
+// worker; slice 0 finishes the tile after adding the other slices' fp32 partials, which they
+// park in a per-CTA scratch slot (split-K for the remainder wave and for skinny M).
 //
 // Reference behaviour covered (file paths inside the reference project):
 //   triton_dist/kernels/dcu/all_gather_gemm.py:98-230   consumer GEMM gated on flags
@@ -27,6 +42,7 @@
 //   triton_dist/kernels/dcu/gemm_reduce_scatter.py:39-135 GEMM, scatter, reduce
 //   triton_dist/kernels/dcu/gemm_allreduce.py:73-181    producer GEMM + consumer reduce
 //   triton_dist/kernels/dcu/ag_tr_pred.py:344-361       table-driven tile order
+//   bench/tune_gemm2.py:69-117                          split-K with fp32 accumulation
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -45,6 +61,7 @@ constexpr int kEpiWarp0 = 2;
 constexpr int kCommWarp0 = 6;
 constexpr int kCommThreads = 128;
 constexpr int kEpiThreads = 128;
+constexpr int kMaxSlices = 8;     // K ranges a remainder tile can be cut into
 
 enum GemmOp : int32_t { OP_PLAIN = 0, OP_AG = 1, OP_RS = 2, OP_AR1 = 3, OP_AR2 = 4 };
 enum EpiMode : int32_t { EPI_STORE = 0, EPI_SWIGLU = 1 };
@@ -55,28 +72,32 @@ enum SchedMode : int32_t {
   SCHED_LIST = 3,      // explicit list of row-major tile ids (repair of flagged tiles)
 };
 
-// Epilogue staging: each accumulator row gets 256 data bytes (128 columns) at a pitch of
-// 272 bytes, so that the 16-byte stores of 8 consecutive rows hit different banks while
-// every row stays contiguous for the bulk copy that ships it.
+// Epilogue staging: 128 accumulator rows x 128 columns of 16-bit data. Used either as two
+// 128 x 64 boxes in the layout a 128-byte-swizzled TMA store expects, or as one padded row per
+// accumulator row (256 data bytes at a pitch of 272 bytes, so that the 16-byte stores of 8
+// consecutive rows hit different banks while every row stays contiguous for a bulk copy).
 constexpr int kStageCols = 128;
 constexpr int kStageRowBytes = kStageCols * 2;
 constexpr int kStagePitch = kStageRowBytes + 16;
 constexpr int kStagingBytes = BM * kStagePitch;
+constexpr int kBoxBytes = BM * 128;      // one 128-row x 64-column box
 
-template <int BN, int kCtaM, bool kStaging>
+template <int BN, int kCtaM, bool kStaging, int kMT>
 struct TileShape {
-  // kCtaM = 2: two CTAs (one cluster) share each tcgen05 MMA; a pair owns a 256 x BN
-  // output tile, every CTA loads its own 128 rows of A and its own BN/2 rows of B.
-  static constexpr int kABytes = BM * BK * 2;
+  // kCtaM = 2: two CTAs (one cluster) share each tcgen05 MMA; every CTA loads its own rows of A
+  // and its own BN/2 rows of B. kMT = 2: 256 rows of A per CTA and stage.
+  static_assert(kMT == 1 || (kCtaM == 2 && kStaging), "256-row CTA tiles run on CTA pairs with staging");
+  static constexpr int kABytes = kMT * BM * BK * 2;
   static constexpr int kBBytes = (BN / kCtaM) * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // 227 KB per CTA: the epilogue staging is only carved out for the operators whose
-  // epilogue publishes tiles to other ranks; the others get a deeper ring instead.
+  // 227 KB per CTA: the epilogue staging is carved out for the operators whose epilogue
+  // publishes tiles to other ranks and for the staged TMA-store epilogue; the others get a
+  // deeper ring instead.
   static constexpr int kStagingUsed = kStaging ? kStagingBytes : 0;
   static constexpr int kStages = (226 * 1024 - kStagingUsed) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;
-  // ring + epilogue staging (one padded 256-byte row per accumulator row) + 1 KB for
-  // barriers and the TMEM slot; the dynamic shared array is declared 1024-byte aligned
+  // ring + epilogue staging + 1 KB for barriers and the TMEM slot; the dynamic shared array is
+  // declared 1024-byte aligned
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingUsed + 1024;
 };
 
@@ -89,7 +110,7 @@ enum ProfSlot : int {
   PROF_EPI_BUSY = 4,         // epilogue: accumulator ready -> accumulator released
   PROF_EPI_PUBLISH = 5,      // epilogue: phase 1 (ship partials, wait for the writes, ticket)
   PROF_EPI_TICKET_WAIT = 6,  // epilogue: phase 2 (waiting for other ranks' partials)
-  PROF_EPI_TILES = 7,        // epilogue: tiles processed (count)
+  PROF_EPI_TILES = 7,        // epilogue: 128-row accumulators processed (count)
   PROF_PUSH_TOTAL = 8,       // communication warps: whole push / collect loop
   PROF_KERNEL = 9,           // CTA lifetime
   PROF_AR_A_WAIT = 10,       // two-shot all-reduce, owner side: waiting for the R partials of owned tiles
@@ -110,6 +131,7 @@ enum ProfSlot : int {
   PROF_TL_COL_SEEN = 24,     // collector: last result ticket seen
   PROF_TL_COMM_START = 25,   // communication warps: entry
   PROF_TL_OWN_IT0 = 26,      // owner: first batch of the reduce loop stored (cold-start cost)
+  PROF_SK_WAIT = 27,         // epilogue: split-K finisher waiting for the other slices' partials
   kProfSlots = 32,
 };
 
@@ -117,6 +139,7 @@ struct alignas(64) GemmParams {
   CUtensorMap tma_a;       // A [rows, K]; for OP_AG this rank's local shard [M_pr, K]
   CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
   CUtensorMap tma_b;       // B [N_rows, K], box 128 rows
+  CUtensorMap tma_c;       // local output (store map, box 128 rows x 64 columns), valid if c_tma
   // Store maps (box 128 rows x 64 columns, 128-byte swizzle) over this rank's slot inside
   // every rank's slot buffer.
   CUtensorMap tma_slot[kMaxRanks];
@@ -126,8 +149,11 @@ struct alignas(64) GemmParams {
   int32_t rank, R;
   int32_t op, epi, sched;
   int32_t cta_m;           // CTAs per scheduling unit along M (1, or 2 for CTA pairs)
-  int32_t unit_m;          // scheduling units along M = ceil(m_tiles / cta_m)
+  int32_t cta_mt;          // 128-row blocks per CTA tile (1 or 2)
+  int32_t sub_tiles;       // 128-row blocks per scheduling unit = cta_m * cta_mt
+  int32_t unit_m;          // scheduling units along M = ceil(m_tiles / sub_tiles)
   int32_t seg_m_tiles;     // units per segment (SCHED_SEGMENT)
+  int32_t raster_g;        // units along M walked together (L2 residency of their A rows)
   int32_t seg_order[kMaxRanks];
   int32_t strided_interleave;  // SCHED_STRIDED: same unit order on every rank (see tile_at)
   const int32_t* order_table;  // optional device table overriding seg_order (R entries)
@@ -140,11 +166,20 @@ struct alignas(64) GemmParams {
 
   void* c;                 // local output (see per-op meaning in the kernel)
   int64_t ldc;
+  int32_t c_tma;           // tma_c is valid: local tiles leave through staged TMA stores
+
+  // ---- split-K of the remainder round ----
+  int32_t sk_tiles;        // scheduling positions (the last ones) that are cut along K
+  int32_t sk_slices;       // K ranges per such position (each on its own worker)
+  float* sk_ws;            // [CTA slot][accumulator block][32-column chunk][8][128 threads] x 16 B
+  uint32_t* sk_flags;      // [CTA slot]: epoch of the last partial parked in the slot
+  uint32_t sk_epoch;       // per-launch value, never repeated on a device
+  int32_t sk_slot_words;   // fp32 words per CTA slot
 
   // ---- OP_AG ----
   const void* a_local;             // this rank's shard (push source)
   void* peer_ws[kMaxRanks];        // workspace base (this round's parity) on every rank
-  uint32_t* peer_ag_flags[kMaxRanks];  // [R][n_chunks] tickets on every rank, indexed by source
+  uint32_t* peer_ag_flags[kMaxRanks];  // [R][ag_flag_stride] tickets on every rank, indexed by source
   uint32_t* ag_counters;           // local [R][n_chunks] part counters
   uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
   int32_t chunk_rows, n_chunks, push_parts;
@@ -155,7 +190,7 @@ struct alignas(64) GemmParams {
 
   // ---- OP_RS / OP_AR* ----
   void* peer_slots[kMaxRanks];     // slot base (this round's parity) on every rank: [R][rows][N]
-  uint32_t* peer_tile_flags[kMaxRanks];  // [R][tiles] tickets on every rank, indexed by source
+  uint32_t* peer_tile_flags[kMaxRanks];  // [R][ticket_stride] tickets on every rank, indexed by source
   int64_t slot_stride;             // elements between two sources' slots
   void* peer_res[kMaxRanks];       // OP_AR2: reduced-result buffer [M][N] on every rank
   uint32_t* peer_res_flags[kMaxRanks];   // OP_AR2: [R][ticket_stride] tickets, indexed by owner
@@ -187,28 +222,30 @@ struct alignas(64) GemmParams {
 // ----------------------------------------------------------------------------
 // Tile order
 // ----------------------------------------------------------------------------
+// A CTA tile: cta_mt consecutive 128-row blocks starting at `m_tile`, one BN-wide column
+// block. `linear` is the ticket index of its first 128-row block (see tile_linear).
 struct TileCoord {
   int m_tile, n_tile, linear, owner_key;
   bool valid;
 };
 
-__host__ __device__ __forceinline__ void raster_grouped(int u, int m_tiles, int n_tiles, int& mt, int& nt) {
-  // Groups of 8 m-tiles walked column by column: a wave of CTAs shares few A
+__host__ __device__ __forceinline__ void raster_grouped(int u, int m_units, int n_tiles, int G, int& mt,
+                                                        int& nt) {
+  // Groups of G row units walked column by column: a wave of CTAs shares few A
   // row blocks and a contiguous run of B column blocks in L2.
-  constexpr int G = 8;
   const int per_group = G * n_tiles;
   const int g = u / per_group;
   const int first_m = g * G;
-  const int gm = min(G, m_tiles - first_m);
+  const int gm = min(G, m_units - first_m);
   const int r = u - g * per_group;
   mt = first_m + r % gm;
   nt = r / gm;
 }
 
-// The schedule enumerates *units*: one unit is one BN-wide column block of cta_m
-// consecutive m-tiles (cta_m = 2 for CTA pairs; CTA `sub` of the pair owns m-tile
-// unit_m * cta_m + sub). `linear` indexes the tile's ticket words; `owner_key` is the
-// unit id that decides the owning rank in the strided (two-shot all-reduce) order.
+// The schedule enumerates *units*: one unit is one BN-wide column block of sub_tiles
+// consecutive 128-row blocks (CTA `sub` of a pair owns blocks unit_m * sub_tiles + sub * cta_mt
+// ...). `owner_key` is the unit id that decides the owning rank in the strided (two-shot
+// all-reduce) order.
 __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos,
                                              int sub) {
   TileCoord t;
@@ -218,7 +255,7 @@ __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const
     const int per_seg = p.seg_m_tiles * p.n_tiles;
     const int si = pos / per_seg;
     const int u = pos - si * per_seg;
-    raster_grouped(u, p.seg_m_tiles, p.n_tiles, um, nt);
+    raster_grouped(u, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
     um += order[si] * p.seg_m_tiles;
   } else if (p.sched == SCHED_STRIDED) {
     const int total = p.unit_m * p.n_tiles;
@@ -230,21 +267,26 @@ __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const
     // over the whole kernel instead of piling up at the end
     ulin = p.strided_interleave ? pos : order[oi] + k * p.R;
     if (ulin >= total) t.valid = false;
-    else raster_grouped(ulin, p.unit_m, p.n_tiles, um, nt);
+    else raster_grouped(ulin, p.unit_m, p.n_tiles, p.raster_g, um, nt);
   } else if (p.sched == SCHED_LIST) {
     const int lin = p.tile_list[pos];
     t.valid = lin >= 0 && lin < p.unit_m * p.n_tiles;
     um = t.valid ? lin / p.n_tiles : 0;
     nt = t.valid ? lin - um * p.n_tiles : 0;
   } else {
-    raster_grouped(pos, p.unit_m, p.n_tiles, um, nt);
+    raster_grouped(pos, p.unit_m, p.n_tiles, p.raster_g, um, nt);
   }
-  t.m_tile = um * p.cta_m + sub;
+  t.m_tile = um * p.sub_tiles + sub * p.cta_mt;
   t.n_tile = nt;
   t.owner_key = ulin;
-  // ownership is keyed by the pre-raster unit id; every tile still has its own ticket
-  t.linear = (p.sched == SCHED_STRIDED) ? ulin * p.cta_m + sub : t.m_tile * p.n_tiles + nt;
+  // ownership is keyed by the pre-raster unit id; every 128-row block still has its own ticket
+  t.linear = (p.sched == SCHED_STRIDED) ? ulin * p.sub_tiles + sub * p.cta_mt : t.m_tile * p.n_tiles + nt;
   return t;
+}
+
+// Ticket index of the h-th 128-row block of a CTA tile.
+__host__ __device__ __forceinline__ int tile_linear(const GemmParams& p, const TileCoord& t, int h) {
+  return (p.sched == SCHED_STRIDED) ? t.linear + h : t.linear + h * p.n_tiles;
 }
 
 __host__ __device__ __forceinline__ int sched_positions(const GemmParams& p) {
@@ -255,14 +297,18 @@ __host__ __device__ __forceinline__ int sched_positions(const GemmParams& p) {
 }
 
 // Static round-robin of the scheduling positions over the workers (a worker is a CTA, or a CTA
-// pair), with one twist: the workers that push the all-gather shard sit out the first `skip`
+// pair), with two twists. The workers that push the all-gather shard sit out the first `skip`
 // rounds (their copy engine is busy and their operand loads are slower meanwhile), so that all
-// workers finish together. Shared by the kernel and the host-side schedule dump.
+// workers finish together. And the positions of the last, partial round (`sk_tiles` of them)
+// are not dealt whole: each is cut into `sk_slices` K ranges, dealt to consecutive workers.
+// Shared by the kernel and the host-side schedule dump.
 struct WorkerSchedule {
   int workers;   // workers in the grid
   int pushers;   // workers 0 .. pushers-1 drive the all-gather push
   int skip;      // rounds the pushers sit out
   int early;     // workers active in the early rounds
+  int dp_positions;   // positions dealt whole
+  int sk_tiles, sk_slices;
   __host__ __device__ int pos_of(int my_worker, int i) const {
     if (my_worker < pushers) return skip * early + i * workers + my_worker;
     if (i < skip) return i * early + (my_worker - pushers);
@@ -280,8 +326,49 @@ __host__ __device__ __forceinline__ WorkerSchedule make_worker_schedule(const Ge
     w.skip = p.push_skip_rounds;
   }
   w.early = w.workers - w.pushers;
+  const int positions = p.comm_only ? 0 : sched_positions(p);
+  w.sk_tiles = (p.sk_slices > 1 && p.sk_tiles <= positions) ? p.sk_tiles : 0;
+  w.sk_slices = w.sk_tiles > 0 ? p.sk_slices : 1;
+  w.dp_positions = positions - w.sk_tiles;
   return w;
 }
+
+// How many of the `positions` fall into the last, partial round of the round-robin (0 = the
+// rounds come out even), for a grid of `workers` workers of which `pushers` skip `skip` rounds.
+__host__ __device__ __forceinline__ int remainder_positions(int positions, int workers, int pushers, int skip) {
+  const int early = workers - pushers;
+  const int head = skip * early;
+  if (positions <= head) return 0;
+  return (positions - head) % workers;
+}
+
+// One piece of work of a worker: scheduling position `pos`, k-blocks [kb0, kb1). slices > 1:
+// the position is shared with slices - 1 other workers; slice 0 finishes the tile.
+struct WorkItem {
+  int pos, kb0, kb1, slice, slices;
+};
+struct WorkIter {
+  int i = 0;
+  bool sk_seen = false;
+  __host__ __device__ bool next(const WorkerSchedule& w, int my_worker, int k_blocks, WorkItem& wi) {
+    if (sk_seen) return false;
+    const int pos = w.pos_of(my_worker, i);
+    if (pos < w.dp_positions) {
+      ++i;
+      wi.pos = pos; wi.kb0 = 0; wi.kb1 = k_blocks; wi.slice = 0; wi.slices = 1;
+      return true;
+    }
+    sk_seen = true;
+    if (my_worker >= w.sk_tiles * w.sk_slices) return false;
+    const int t = my_worker / w.sk_slices, s = my_worker - t * w.sk_slices;
+    wi.pos = w.dp_positions + t;
+    wi.kb0 = static_cast<int>(static_cast<long long>(s) * k_blocks / w.sk_slices);
+    wi.kb1 = static_cast<int>(static_cast<long long>(s + 1) * k_blocks / w.sk_slices);
+    wi.slice = s;
+    wi.slices = w.sk_slices;
+    return true;
+  }
+};
 
 // ----------------------------------------------------------------------------
 // Epilogue helpers
@@ -402,11 +489,13 @@ __device__ __forceinline__ void stage_row32_swizzled(uint8_t* staging, int r, in
 
 // Collective decision of the four epilogue warps. The flag is sticky; the
 // second barrier keeps a fast warp from raising it for a later check while a
-// slow warp has not read it yet, so all 128 threads always agree.
-__device__ __forceinline__ bool epi_vote(volatile int32_t* flag, bool my_ok) {
-  if (!my_ok) *flag = 1;
+// slow warp has not read it yet, so all 128 threads always agree. flags[3] carries a
+// value that thread 0 of the group wrote before the call (read by all between the barriers).
+__device__ __forceinline__ bool epi_vote(volatile int32_t* flags, bool my_ok, int32_t* carried = nullptr) {
+  if (!my_ok) flags[0] = 1;
   named_bar_sync(2, kEpiThreads);
-  const bool dead = *flag != 0;
+  const bool dead = flags[0] != 0;
+  if (carried) *carried = flags[3];
   named_bar_sync(2, kEpiThreads);
   return !dead;
 }
@@ -416,10 +505,10 @@ __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __e
 // ----------------------------------------------------------------------------
 // The kernel
 // ----------------------------------------------------------------------------
-template <int BN, bool kBf16, int kCtaM, bool kStaging>
+template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __restrict__ pv) {
-  using TS = TileShape<BN, kCtaM, kStaging>;
+  using TS = TileShape<BN, kCtaM, kStaging, kMT>;
   static_assert(kCtaM == 1 || BN == 256, "CTA pairs are built for 256-wide tiles only");
   // With pv != nullptr the launch emulates several ranks on one GPU: grid.y
   // indexes the rank and each rank reads its own parameter block.
@@ -437,7 +526,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   uint64_t* push_bar = drain_bar + 1;            // 2 barriers of the all-gather push ring
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + 2);
   int32_t* s_order = reinterpret_cast<int32_t*>(tmem_slot + 4);
-  // s_flags[0]: an epilogue warp gave up; s_flags[1]: outcome of the comm warps' last wait
+  // s_flags[0]: an epilogue warp gave up; [1]: outcome of the comm warps' last wait; [2]: the
+  // all-gather push of this CTA no longer uses the staging area; [3]: the epilogue's copy of [2]
   volatile int32_t* s_flags = s_order + kMaxRanks;
 
   const int warp = threadIdx.x >> 5;
@@ -448,7 +538,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   const bool leader = sub == 0;
   const WorkerSchedule wsched = make_worker_schedule(p, static_cast<int>(gridDim.x), kCtaM);
   const int my_worker = static_cast<int>(blockIdx.x) / kCtaM;
-  auto pos_of = [&](int i) -> int { return wsched.pos_of(my_worker, i); };
+  const int push_grid = (p.push_ctas > 0 && p.push_ctas < static_cast<int>(gridDim.x))
+                            ? p.push_ctas : static_cast<int>(gridDim.x);
+  const bool pushes = kStaging && p.op == OP_AG && p.R > 1 && !p.skip_comm &&
+                      static_cast<int>(blockIdx.x) < push_grid;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TS::kStages; ++s) {
@@ -464,6 +557,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     mbar_init(&push_bar[1], 1);
     s_flags[0] = 0;
     s_flags[1] = 1;
+    s_flags[2] = pushes ? 0 : 1;
+    s_flags[3] = 0;
     mbar_fence_init();
   }
   if (threadIdx.x < kMaxRanks) {
@@ -485,8 +580,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-  // comm_only: no tiles are computed, only the communication warps run (push timing)
-  const int positions = p.comm_only ? 0 : sched_positions(p);
   const WaitEnv env = p.env;
   uint64_t* const prof = p.prof ? p.prof + static_cast<int64_t>(blockIdx.x) * kProfSlots : nullptr;
   const uint64_t t_kernel0 = prof ? globaltimer_ns() : 0;
@@ -513,10 +606,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool swiglu = p.epi == EPI_SWIGLU;
       const int up_row0 = p.swiglu_up_row0;
       const CUtensorMap* const bmap = &p.tma_b;
-      for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
-        const TileCoord t = tile_at(p, s_order, pos, sub);
+      WorkIter wit;
+      WorkItem wi;
+      while (ok && wit.next(wsched, my_worker, k_blocks, wi)) {
+        const TileCoord t = tile_at(p, s_order, wi.pos, sub);
         if (!t.valid) continue;
-        const int m0 = t.m_tile * BM;
+        const int m0 = t.m_tile * BM;          // first of the CTA tile's kMT * 128 rows
         const int n0 = t.n_tile * BN;
         const CUtensorMap* amap = &p.tma_a;
         int a_row = m0;
@@ -527,9 +622,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           } else {
             amap = &p.tma_a_ws;
             if (!p.skip_comm) {
-              // every chunk the 128-row block touches must have landed
+              // every chunk the CTA tile's rows touch must have landed
               const int r_lo = m0 - src * p.m_per_rank;
-              const int r_hi = min(r_lo + BM, p.m_per_rank) - 1;
+              const int r_hi = min(r_lo + kMT * BM, p.m_per_rank) - 1;
               for (int ck = r_lo / p.chunk_rows; ok && ck <= r_hi / p.chunk_rows; ++ck) {
                 if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
                 const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.ag_flag_stride + ck;
@@ -553,7 +648,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int b_row_pair = swiglu
             ? (sub == 0 ? t.n_tile * (BN / 2) : up_row0 + t.n_tile * (BN / 2))
             : n0 + sub * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (probe == 1) {
             if (loads_issued >= TS::kStages) break;   // ring filled once, then idle
             ++loads_issued;
@@ -572,7 +667,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           if constexpr (kCtaM == 2) {
             // the leader's barrier collects the bytes of both CTAs' loads
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * TS::kStageBytes);
-            tma_load_2d_pair(sa, amap, &full_bar[stage], kb * BK, a_row);
+#pragma unroll
+            for (int h = 0; h < kMT; ++h)
+              tma_load_2d_pair(sa + h * (BM * BK * 2), amap, &full_bar[stage], kb * BK, a_row + h * BM);
             tma_load_2d_pair(sb, bmap, &full_bar[stage], kb * BK, b_row_pair);
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], TS::kStageBytes);
@@ -630,65 +727,135 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const uint64_t da0 = umma_desc_k_sw128(smem_u32(ring));
       const uint64_t db0 = umma_desc_k_sw128(smem_u32(ring) + TS::kABytes);
       constexpr uint64_t kDescStage = static_cast<uint64_t>(TS::kStageBytes >> 4);
-      uint64_t da = da0, db = db0;
-      for (int si = 0, pos = pos_of(0); ok && pos < positions; pos = pos_of(++si)) {
-        const TileCoord t = tile_at(p, s_order, pos, sub);
-        if (!t.valid) continue;
-        const int buf = it & 1;
-        const uint32_t use = static_cast<uint32_t>(it >> 1);
-        if (prof && !mbar_try_wait(&tmem_empty_bar[buf], (use & 1u) ^ 1u)) {
-          const uint64_t tw = globaltimer_ns();
-          ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
-          acc_t += globaltimer_ns() - tw;
-        } else {
-          ok = wait_mbar(&tmem_empty_bar[buf], (use & 1u) ^ 1u, env, SITE_TMEM_EMPTY, buf);
+      constexpr uint64_t kDescRows = static_cast<uint64_t>((BM * BK * 2) >> 4);   // next 128 rows of A
+      // four MMAs of one 64-wide k-block into accumulator d_tmem; `fresh` overwrites it
+      auto mma4 = [&](uint32_t d_tmem, uint64_t da, uint64_t db, bool fresh) {
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // +32 bytes per K step inside the 128-byte swizzle row
+          if constexpr (kCtaM == 2)
+            umma_f16_ss_pair(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2),
+                             idesc, (fresh && k == 0) ? 0u : 1u);
+          else
+            umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
+                        (fresh && k == 0) ? 0u : 1u);
         }
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (probe == 1 && kblocks_done >= TS::kStages) {
-            // tensor-pipe ceiling: the stage was filled in the first pass and stays resident
-          } else if (prof && !mbar_try_wait(&full_bar[stage], phase)) {
-            const uint64_t tw = globaltimer_ns();
-            ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
-            acc_f += globaltimer_ns() - tw;
-          } else if (!mbar_try_wait(&full_bar[stage], phase)) {
-            ok = wait_mbar(&full_bar[stage], phase, env, SITE_PIPE_FULL, stage);
+      };
+      // frees the smem stage (in both CTAs of a pair) when the MMAs issued so far retire
+      auto commit_stage = [&](uint32_t s) {
+        if constexpr (kCtaM == 2) umma_commit_pair_both(&empty_bar[s]);
+        else umma_commit(&empty_bar[s]);
+      };
+      // accumulator complete (each CTA of a pair reads its own 128 rows)
+      auto commit_acc = [&](int b) {
+        if constexpr (kCtaM == 2) umma_commit_pair_both(&tmem_full_bar[b]);
+        else umma_commit(&tmem_full_bar[b]);
+      };
+      auto wait_full = [&](uint32_t s, uint32_t ph) -> bool {
+        if (mbar_try_wait(&full_bar[s], ph)) return true;
+        const uint64_t tw = prof ? globaltimer_ns() : 0;
+        const bool r = wait_mbar(&full_bar[s], ph, env, SITE_PIPE_FULL, s);
+        if (prof) acc_f += globaltimer_ns() - tw;
+        return r;
+      };
+      auto wait_acc_free = [&](int b, uint32_t par) -> bool {
+        if (mbar_try_wait(&tmem_empty_bar[b], par)) return true;
+        const uint64_t tw = prof ? globaltimer_ns() : 0;
+        const bool r = wait_mbar(&tmem_empty_bar[b], par, env, SITE_TMEM_EMPTY, b);
+        if (prof) acc_t += globaltimer_ns() - tw;
+        return r;
+      };
+      WorkIter wit;
+      WorkItem wi;
+      while (ok && wit.next(wsched, my_worker, k_blocks, wi)) {
+        const TileCoord t = tile_at(p, s_order, wi.pos, sub);
+        if (!t.valid) continue;
+        const int nkb = wi.kb1 - wi.kb0;
+        if constexpr (kMT == 1) {
+          // the two accumulators double-buffer whole tiles
+          const int buf = it & 1;
+          const uint32_t use = static_cast<uint32_t>(it >> 1);
+          ok = wait_acc_free(buf, (use & 1u) ^ 1u);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+          for (int j = 0; j < nkb; ++j) {
+            if (!(probe == 1 && kblocks_done >= TS::kStages)) {
+              // (probe 1, tensor-pipe ceiling: stages filled in the first pass stay resident)
+              ok = wait_full(stage, phase);
+              if (!ok) break;
+            }
+            if (probe != 0) {
+              ++kblocks_done;
+              if (probe == 2) {
+                // operand-feed ceiling: hand the stage straight back to the producer(s)
+                mbar_arrive(&empty_bar[stage]);
+                if constexpr (kCtaM == 2) mbar_arrive_cluster(&empty_bar[stage], 1u);
+                if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+                continue;
+              }
+            }
+            tc_fence_after_sync();
+            mma4(d_tmem, da0 + stage * kDescStage, db0 + stage * kDescStage, j == 0);
+            commit_stage(stage);
+            if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          if (probe != 0) {
-            ++kblocks_done;
-            if (probe == 2) {
-              // operand-feed ceiling: hand the stage straight back to the producer(s)
-              mbar_arrive(&empty_bar[stage]);
-              if constexpr (kCtaM == 2) mbar_arrive_cluster(&empty_bar[stage], 1u);
-              if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
-              continue;
-            }
-          }
+          commit_acc(buf);
+        } else {
+          // One accumulator per 128-row half, both used by every tile. Half 0 is drained first
+          // by the epilogue, so its MMAs of the first k-blocks are issued as soon as accumulator
+          // 0 is free, while accumulator 1 is still being drained; the stages stay occupied
+          // until half 1 has consumed them too.
+          const uint32_t par_free = static_cast<uint32_t>(it & 1) ^ 1u;
+          const int ahead = (probe != 0) ? 0 : min(static_cast<int>(TS::kStages), nkb);
+          ok = wait_acc_free(0, par_free);
+          if (!ok) break;
           tc_fence_after_sync();
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // +32 bytes per K step inside the 128-byte swizzle row
-            if constexpr (kCtaM == 2)
-              umma_f16_ss_pair(d_tmem, da + static_cast<uint64_t>(k * 2),
-                               db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * 2),
-                          db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+          uint32_t s1 = stage, ph1 = phase;
+          for (int j = 0; j < ahead; ++j) {
+            ok = wait_full(s1, ph1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            mma4(tmem_base, da0 + s1 * kDescStage, db0 + s1 * kDescStage, j == 0);
+            if (j == nkb - 1) commit_acc(0);
+            if (++s1 == TS::kStages) { s1 = 0; ph1 ^= 1u; }
           }
-          // frees the smem stage (in both CTAs of a pair) when these MMAs retire
-          if constexpr (kCtaM == 2) umma_commit_pair_both(&empty_bar[stage]);
-          else umma_commit(&empty_bar[stage]);
-          da += kDescStage;
-          db += kDescStage;
-          if (++stage == TS::kStages) { stage = 0; phase ^= 1u; da = da0; db = db0; }
+          if (!ok) break;
+          ok = wait_acc_free(1, par_free);
+          if (!ok) break;
+          tc_fence_after_sync();
+          for (int j = 0; j < ahead; ++j) {
+            mma4(tmem_base + BN, da0 + stage * kDescStage + kDescRows, db0 + stage * kDescStage, j == 0);
+            commit_stage(stage);
+            if (j == nkb - 1) commit_acc(1);
+            if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+          }
+          for (int j = ahead; j < nkb; ++j) {
+            if (!(probe == 1 && kblocks_done >= TS::kStages)) {
+              ok = wait_full(stage, phase);
+              if (!ok) break;
+            }
+            if (probe != 0) {
+              ++kblocks_done;
+              if (probe == 2) {
+                mbar_arrive(&empty_bar[stage]);
+                mbar_arrive_cluster(&empty_bar[stage], 1u);
+                if (j == nkb - 1) { commit_acc(0); commit_acc(1); }
+                if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+                continue;
+              }
+            }
+            tc_fence_after_sync();
+            mma4(tmem_base, da0 + stage * kDescStage, db0 + stage * kDescStage, j == 0);
+            if (j == nkb - 1) commit_acc(0);
+            mma4(tmem_base + BN, da0 + stage * kDescStage + kDescRows, db0 + stage * kDescStage, j == 0);
+            commit_stage(stage);
+            if (j == nkb - 1) commit_acc(1);
+            if (++stage == TS::kStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
         }
-        if (!ok) break;
-        // accumulator complete (each CTA of a pair reads its own 128 rows)
-        if constexpr (kCtaM == 2) umma_commit_pair_both(&tmem_full_bar[buf]);
-        else umma_commit(&tmem_full_bar[buf]);
         ++it;
       }
       if (prof) {
@@ -712,45 +879,128 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   else if (warp < kCommWarp0) {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int etid = (warp - kEpiWarp0) * 32 + lane;
+    const int r_in_tile = q * 32 + lane;
     const int64_t ldc = p.ldc;
     const int tiles = p.ticket_stride;                  // ticket words per source
     const bool multi = p.R > 1;
-    uint64_t acc_busy = 0, acc_pub = 0, acc_tick = 0, n_tiles_done = 0;
+    // scratch slots of the split-K partials are indexed by the CTA's place in the launch
+    const int slot0 = static_cast<int>(blockIdx.y * gridDim.x);
+    const int my_slot = slot0 + static_cast<int>(blockIdx.x);
+    uint64_t acc_busy = 0, acc_pub = 0, acc_tick = 0, acc_sk = 0, n_tiles_done = 0;
     int it = 0;
-    for (int si = 0, pos = pos_of(0); pos < positions; pos = pos_of(++si)) {
-      const TileCoord t = tile_at(p, s_order, pos, sub);
+    bool alive = true;
+    WorkIter wit;
+    WorkItem wi;
+    while (alive && wit.next(wsched, my_worker, p.k_blocks, wi)) {
+      const TileCoord t = tile_at(p, s_order, wi.pos, sub);
       if (!t.valid) continue;
-      const int buf = it & 1;
-      const uint32_t use = static_cast<uint32_t>(it >> 1);
+      for (int h = 0; alive && h < kMT; ++h) {
+      const int buf = (kMT == 2) ? h : (it & 1);
+      const uint32_t par = (kMT == 2) ? static_cast<uint32_t>(it & 1) : static_cast<uint32_t>((it >> 1) & 1);
+      const int m_tile = t.m_tile + h;
+      const int lin = tile_linear(p, t, h);
       // The four epilogue warps decide together whether to go on: a warp that
       // gave up must never leave the others parked at a named barrier.
       // one lane per warp polls (the other 31 sleep at the warp barrier): the epilogue warps
       // spend most of the kernel here, and idle polling costs power the tensor cores need
       bool acc_ready = true;
-      if (lane == 0) acc_ready = wait_mbar(&tmem_full_bar[buf], use & 1u, env, SITE_TMEM_FULL, buf);
+      if (lane == 0) acc_ready = wait_mbar(&tmem_full_bar[buf], par, env, SITE_TMEM_FULL, buf);
       acc_ready = __shfl_sync(0xFFFFFFFFu, acc_ready ? 1 : 0, 0) != 0;
-      if (!epi_vote(&s_flags[0], acc_ready)) break;
+      if (etid == 0) s_flags[3] = s_flags[2];
+      int32_t stg = 0;
+      if (!epi_vote(s_flags, acc_ready, &stg)) { alive = false; break; }
+      const bool staging_free = kStaging && stg != 0;   // not in use by this CTA's all-gather push
       tc_fence_after_sync();
       const uint64_t t_epi0 = (prof && etid == 0) ? globaltimer_ns() : 0;
       if (prof && etid == 0) prof[PROF_TL_ACC_READY] = t_epi0 - t_kernel0;
 
-      const int row = t.m_tile * BM + q * 32 + lane;
+      const int row = m_tile * BM + r_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(buf * BN);
+      bool released = false;
+      // accumulator drained: hand the TMEM buffer back to the MMA warp
+      auto release_acc = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtaM == 2) mbar_arrive_leader(&tmem_empty_bar[buf]);
+          else mbar_arrive(&tmem_empty_bar[buf]);
+        }
+        released = true;
+      };
+
+      // ---- split-K: slices other than 0 park their fp32 accumulator and are done ----------
+      if (wi.slices > 1) {
+        // layout of a slot: [accumulator block][32-column chunk][16-byte piece][thread]
+        if (wi.slice > 0) {
+          float* dst = p.sk_ws + static_cast<int64_t>(my_slot) * p.sk_slot_words + h * (BM * BN);
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              st_global_v4(dst + ((c * 8 + v) * kEpiThreads + etid) * 4,
+                           make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]));
+          }
+          release_acc();
+          if (h == kMT - 1) {
+            // the barrier orders all 128 threads' stores before the one release below
+            named_bar_sync(2, kEpiThreads);
+            if (etid == 0) st_release_gpu(p.sk_flags + my_slot, p.sk_epoch);
+          }
+          if (prof && etid == 0) {
+            acc_busy += globaltimer_ns() - t_epi0;
+            ++n_tiles_done;
+          }
+          continue;
+        }
+        // slice 0: add the partials of slices 1 .. slices-1 (the next workers) in that order
+        const uint64_t t_sk0 = (prof && etid == 0) ? globaltimer_ns() : 0;
+        bool ok = true;
+        if (etid == 0) {
+          for (int s = 1; ok && s < wi.slices; ++s)
+            ok = wait_flag_ge(p.sk_flags + slot0 + (my_worker + s) * kCtaM + sub, p.sk_epoch, env,
+                              SITE_SPLITK, s);
+        }
+        if (!epi_vote(s_flags, ok)) { alive = false; break; }
+        if (prof && etid == 0) acc_sk += globaltimer_ns() - t_sk0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          for (int s = 1; s < wi.slices; ++s) {
+            const float* src = p.sk_ws +
+                static_cast<int64_t>(slot0 + (my_worker + s) * kCtaM + sub) * p.sk_slot_words + h * (BM * BN);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              const uint4 x = ld_global_cg_v4(src + ((c * 8 + v) * kEpiThreads + etid) * 4);
+              r[v * 4 + 0] = __float_as_uint(__uint_as_float(r[v * 4 + 0]) + __uint_as_float(x.x));
+              r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + __uint_as_float(x.y));
+              r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + __uint_as_float(x.z));
+              r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + __uint_as_float(x.w));
+            }
+          }
+          tmem_st_32x32b_x32(taddr + c * 32, r);
+        }
+        tmem_st_wait();
+      }
 
       // ---- routing: which rank keeps this lane's row / this tile --------------
       int owner = p.rank;
       bool tile_reduces = false;            // uniform over the CTA
       bool tile_publishes = false;          // uniform over the CTA
       int o_lo = 0, o_hi = 0;
-      // a pair's second CTA can fall past the last row block when m_tiles is odd
-      const bool tile_has_rows = t.m_tile * BM < p.M;
+      // a CTA tile's later blocks can fall past the last row block
+      const bool tile_has_rows = m_tile * BM < p.M;
       if (multi && tile_has_rows) {
         if (p.op == OP_RS) {
           owner = min(row / p.m_per_rank, p.R - 1);
-          o_lo = (t.m_tile * BM) / p.m_per_rank;
-          o_hi = min((min(t.m_tile * BM + BM, p.M) - 1) / p.m_per_rank, p.R - 1);
+          o_lo = (m_tile * BM) / p.m_per_rank;
+          o_hi = min((min(m_tile * BM + BM, p.M) - 1) / p.m_per_rank, p.R - 1);
           tile_reduces = (o_lo <= p.rank && p.rank <= o_hi);
           tile_publishes = !(o_lo == p.rank && o_hi == p.rank);
         } else if (p.op == OP_AR2) {
@@ -764,6 +1014,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           tile_publishes = true;
         }
       }
+      // the accumulator is needed after the publish phase only where this rank adds the
+      // peers' partials to it (its own rows of a reduce-scatter tile)
+      const bool acc_needed_later = tile_reduces && p.op == OP_RS;
 
       // ---- phase 1: publish 16-bit partials into other ranks' slots --------------
       // Always before any wait: two owners of one mixed tile would otherwise wait
@@ -775,9 +1028,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           // The whole tile goes to one rank (or, one-shot, to all of them): stage 128 columns
           // at a time in TMA layout and let one thread ship them with 2-D tiled stores
           // (two 128 x 64 boxes per destination) -- few large copy-engine operations.
-          const int r_in_tile = q * 32 + lane;
           const int dest = (p.op == OP_RS) ? o_lo : owner;      // uniform over the CTA
-          const int row0 = (p.op == OP_RS) ? t.m_tile * BM - dest * p.m_per_rank : t.m_tile * BM;
+          const int row0 = (p.op == OP_RS) ? m_tile * BM - dest * p.m_per_rank : m_tile * BM;
           for (int half = 0; half < BN / kStageCols; ++half) {
             const int col0 = t.n_tile * BN + half * kStageCols;
             if (col0 >= p.N) break;
@@ -799,33 +1051,36 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               if (p.op == OP_AR1) {
                 for (int d = 0; d < p.R; ++d) {
                   tma_store_2d(&p.tma_slot[d], staging, col0, row0);
-                  tma_store_2d(&p.tma_slot[d], staging + BM * 128, col0 + 64, row0);
+                  tma_store_2d(&p.tma_slot[d], staging + kBoxBytes, col0 + 64, row0);
                 }
               } else {
                 tma_store_2d(&p.tma_slot[dest], staging, col0, row0);
-                tma_store_2d(&p.tma_slot[dest], staging + BM * 128, col0 + 64, row0);
+                tma_store_2d(&p.tma_slot[dest], staging + kBoxBytes, col0 + 64, row0);
               }
               tma_store_commit();
             }
           }
+          // the partial is in shared memory (or on its way): the MMAs of the next tile may
+          // overwrite the accumulator while the stores complete and the ticket goes out
+          if (!acc_needed_later) release_acc();
           if (prof && etid == 0) prof[PROF_TL_STAGED] = globaltimer_ns() - t_kernel0;
           if (etid == 0) tma_store_wait_all<0>();      // every byte has been written
           if (prof && etid == 0) prof[PROF_TL_STORED] = globaltimer_ns() - t_kernel0;
         } else {
-        // Each thread owns one accumulator row: it converts 128 columns into its staging
+          // Each thread owns one accumulator row: it converts 128 columns into its staging
           // row, then ships the 256 contiguous bytes to every destination with one bulk
           // copy each (large NVLink writes instead of scattered 16-byte stores).
-          uint8_t* my_stage = staging + (q * 32 + lane) * kStagePitch;
+          uint8_t* my_stage = staging + r_in_tile * kStagePitch;
           for (int half = 0; half < BN / kStageCols; ++half) {
             const int col0 = t.n_tile * BN + half * kStageCols;
             tma_store_wait_read<0>();          // my previous copies have read this row
-  #pragma unroll 1
+#pragma unroll 1
             for (int c = 0; c < kStageCols / 32; ++c) {
               uint32_t r[32];
               tmem_ld_32x32b_x32(taddr + half * kStageCols + c * 32, r);
               tmem_ld_wait();
               uint4* d4 = reinterpret_cast<uint4*>(my_stage + c * 64);
-  #pragma unroll
+#pragma unroll
               for (int v = 0; v < 4; ++v) {
                 uint4 o;
                 o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
@@ -854,6 +1109,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             }
             tma_store_commit();
           }
+          if (!acc_needed_later) release_acc();
           tma_store_wait_all<0>();             // every byte has been written
         }
         // Every thread has seen its own bulk stores complete. The barrier orders them before the
@@ -863,12 +1119,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (p.op == OP_RS) {
           const int o = o_lo + etid;
           if (o <= o_hi && o != p.rank)
-            st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + t.linear, p.round);
+            st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + lin, p.round);
         } else if (p.op == OP_AR1) {
           if (etid < p.R && etid != p.rank)
-            st_release_sys(p.peer_tile_flags[etid] + p.rank * tiles + t.linear, p.round);
+            st_release_sys(p.peer_tile_flags[etid] + p.rank * tiles + lin, p.round);
         } else if (etid == 0) {
-          st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + t.linear, p.round);
+          st_release_sys(p.peer_tile_flags[owner] + p.rank * tiles + lin, p.round);
         }
         if (prof && etid == 0) prof[PROF_TL_FLAGGED] = globaltimer_ns() - t_kernel0;
       }
@@ -880,12 +1136,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         if (etid == 0) {
           for (int s = 0; ok && s < p.R; ++s) {
             if (s == p.rank) continue;
-            ok = wait_flag_ge(p.peer_tile_flags[p.rank] + s * tiles + t.linear, p.round, env,
-                              p.op == OP_RS ? SITE_RS_TILE : SITE_AR_TILE, (s << 24) | t.linear);
+            ok = wait_flag_ge(p.peer_tile_flags[p.rank] + s * tiles + lin, p.round, env,
+                              p.op == OP_RS ? SITE_RS_TILE : SITE_AR_TILE, (s << 24) | lin);
           }
         }
         // the barriers inside the vote also order the slot reads after the acquire
-        if (!epi_vote(&s_flags[0], ok)) break;
+        if (!epi_vote(s_flags, ok)) { alive = false; break; }
       }
 
       if (prof && etid == 0) {
@@ -903,6 +1159,58 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int n_cols = p.N;
         uint8_t* const c_base = reinterpret_cast<uint8_t*>(p.c);
         const bool local_tile = !multi || op == OP_PLAIN || op == OP_AG;
+        if (local_tile && staging_free && p.c_tma) {
+          // Local result: convert 64 columns at a time into one of two swizzled 128 x 64 boxes
+          // and let one thread ship the box with a 2-D tiled store (rows and columns past the
+          // end of c are clipped by the copy engine). The accumulator is free as soon as its
+          // last columns are in shared memory; nobody waits for the stores here.
+          const int out_col0 = swiglu ? t.n_tile * (BN / 2) : t.n_tile * BN;
+          const int boxes = swiglu ? BN / 128 : BN / 64;
+#pragma unroll 1
+          for (int j = 0; j < boxes; ++j) {
+            const int ocol = out_col0 + j * 64;
+            if (ocol >= n_cols) break;
+            uint8_t* box = staging + (j & 1) * kBoxBytes;
+            // the store that last read this box was issued two groups ago (any group for j = 0)
+            if (etid == 0) {
+              if (j == 0) tma_store_wait_read<0>();
+              else tma_store_wait_read<1>();
+            }
+            named_bar_sync(2, kEpiThreads);
+            if (swiglu) {
+              // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
+#pragma unroll 1
+              for (int cc = 0; cc < 2; ++cc) {
+                uint32_t g[32], u[32];
+                tmem_ld_32x32b_x32(taddr + j * 64 + cc * 32, g);
+                tmem_ld_32x32b_x32(taddr + BN / 2 + j * 64 + cc * 32, u);
+                tmem_ld_wait();
+                float acc[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) acc[e] = silu(__uint_as_float(g[e])) * __uint_as_float(u[e]);
+                stage_row32_swizzled<kBf16>(box, r_in_tile, cc, acc);
+              }
+            } else {
+              uint32_t r0[32], r1[32];
+              tmem_ld_32x32b_x32(taddr + j * 64, r0);
+              tmem_ld_32x32b_x32(taddr + j * 64 + 32, r1);
+              tmem_ld_wait();
+              float acc[32];
+#pragma unroll
+              for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r0[e]);
+              stage_row32_swizzled<kBf16>(box, r_in_tile, 0, acc);
+#pragma unroll
+              for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r1[e]);
+              stage_row32_swizzled<kBf16>(box, r_in_tile, 1, acc);
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(2, kEpiThreads);
+            if (etid == 0) {
+              tma_store_2d(&p.tma_c, box, ocol, m_tile * BM);
+              tma_store_commit();
+            }
+          }
+        } else {
         for (int c = 0; c < BN / 32; ++c) {
           if (swiglu && c >= BN / 64) break;
           const int ocol = swiglu ? t.n_tile * (BN / 2) + c * 32 : t.n_tile * BN + c * 32;
@@ -954,27 +1262,25 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             }
           }
         }
+        }
       }
 
-      // accumulator drained: hand the TMEM buffer back to the MMA warp
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (kCtaM == 2) mbar_arrive_leader(&tmem_empty_bar[buf]);
-        else mbar_arrive(&tmem_empty_bar[buf]);
-      }
+      if (!released) release_acc();
       if (prof && etid == 0) {
         acc_busy += globaltimer_ns() - t_epi0;
         ++n_tiles_done;
       }
-
+      }   // 128-row blocks of the CTA tile
       ++it;
     }
+    // staged stores must have read shared memory before the CTA goes away
+    if (kStaging && etid == 0) tma_store_wait_all<0>();
     if (prof && etid == 0) {
       prof[PROF_EPI_BUSY] = acc_busy;
       prof[PROF_EPI_PUBLISH] = acc_pub;
       prof[PROF_EPI_TICKET_WAIT] = acc_tick;
       prof[PROF_EPI_TILES] = n_tiles_done;
+      prof[PROF_SK_WAIT] = acc_sk;
       prof[PROF_EPI_DONE_AT] = globaltimer_ns() - t_kernel0;
     }
   }
@@ -1045,9 +1351,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             st_release_sys(p.peer_ag_flags[dest] + p.rank * p.ag_flag_stride + ck, p.round);
           }
         }
+        // every copy of this thread has completed: the staging area now belongs to the epilogue
+        __threadfence_block();
+        s_flags[2] = 1;
       }
     } else if (p.op == OP_AR2 && p.R > 1) {
-      const int tickets = p.unit_m * p.cta_m * p.n_tiles;
+      const int tickets = p.unit_m * p.sub_tiles * p.n_tiles;
       const int units = p.unit_m * p.n_tiles;
       bool ok = true;
       // ---- phase A: finish the tiles this rank owns (unit % R == rank), spread over all CTAs --
@@ -1058,12 +1367,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       if (cprof) prof[PROF_TL_COMM_START] = globaltimer_ns() - t_kernel0;
       uint64_t acc_aw = 0, acc_ak = 0, acc_bw = 0, acc_bc = 0;
       for (int unit = p.rank; ok && unit < units; unit += p.R) {
-        for (int subt = 0; ok && subt < p.cta_m; ++subt, ++owned_seq) {
+        for (int subt = 0; ok && subt < p.sub_tiles; ++subt, ++owned_seq) {
           if (owned_seq % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
-          const int lin = unit * p.cta_m + subt;
+          const int lin = unit * p.sub_tiles + subt;
           int um, nt;
-          raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
-          const int mt = um * p.cta_m + subt;
+          raster_grouped(unit, p.unit_m, p.n_tiles, p.raster_g, um, nt);
+          const int mt = um * p.sub_tiles + subt;
           if (mt * BM >= p.M) continue;
           const uint64_t ta0 = cprof ? globaltimer_ns() : 0;
           if (ctid == 0) s_flags[1] = 1;
@@ -1193,11 +1502,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       }
       // ---- phase B: collect the tiles the other ranks finished ------------------------------
       for (int lin = blockIdx.x; ok && lin < tickets; lin += gridDim.x) {
-        const int unit = lin / p.cta_m;
+        const int unit = lin / p.sub_tiles;
         if (unit % p.R == p.rank) continue;
         int um, nt;
-        raster_grouped(unit, p.unit_m, p.n_tiles, um, nt);
-        const int mt = um * p.cta_m + (lin - unit * p.cta_m);
+        raster_grouped(unit, p.unit_m, p.n_tiles, p.raster_g, um, nt);
+        const int mt = um * p.sub_tiles + (lin - unit * p.sub_tiles);
         if (mt * BM >= p.M) continue;         // nothing is ever published for an empty row block
         const uint64_t tb0 = cprof ? globaltimer_ns() : 0;
         if (ctid == 0)
@@ -1250,6 +1559,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       }
     }
   }
+
 
   if (prof && threadIdx.x == kCommWarp0 * 32)
     prof[PROF_PUSH_TOTAL] = globaltimer_ns() - (p.prof ? t_kernel0 : 0);

@@ -68,6 +68,7 @@ struct GemmPlan {
   int bn;
   bool bf16;
   int cta_m;
+  int cta_mt;
   int grid_x;
   GemmParams* dev_params = nullptr;   // emulated multi-rank launches only
 };
@@ -90,19 +91,19 @@ static int num_sms() {
   return n;
 }
 
-template <int BN, bool kBf16, int kCtaM, bool kStaging>
+template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
 static void set_attr_once() {
   static bool done = false;
   if (!done) {
-    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16, kCtaM, kStaging>,
+    check(cudaFuncSetAttribute(fused_gemm_kernel<BN, kBf16, kCtaM, kStaging, kMT>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               TileShape<BN, kCtaM, kStaging>::kSmemBytes),
+                               TileShape<BN, kCtaM, kStaging, kMT>::kSmemBytes),
           "cudaFuncSetAttribute(smem)");
     done = true;
   }
 }
 
-// CTA pairs (one 2-CTA tcgen05 MMA per 256 x 256 output tile) where the schedule allows.
+// CTA pairs (one 2-CTA tcgen05 MMA per 256-wide output tile) where the schedule allows.
 static int choose_cta_m(const GemmPlanDesc& d) {
   const int mt = (d.M + BM - 1) / BM;
   bool pair = d.allow_pair && d.bn == 256 && mt >= 2 && d.sched != SCHED_LIST;
@@ -110,8 +111,21 @@ static int choose_cta_m(const GemmPlanDesc& d) {
   return pair ? 2 : 1;
 }
 
+// 128-row blocks per CTA: 2 (a 512 x 256 tile per CTA pair) where there are enough rows and the
+// schedule's row segments are whole numbers of such tiles.
+static int choose_cta_mt(const GemmPlanDesc& d, int cta_m) {
+  const int mt = (d.M + BM - 1) / BM;
+  if (cta_m != 2 || !d.allow_wide || mt < 4) return 1;
+  if (d.sched == SCHED_SEGMENT && ((mt / d.R) % 4 != 0)) return 1;
+  // reduce-scatter tiles whose rows belong to several owners keep the 128-row granularity
+  if (d.op == OP_RS && d.R > 1 && d.sched != SCHED_SEGMENT) return 1;
+  return 2;
+}
+
+constexpr int kMinKBlocksPerSlice = 8;    // a K range shorter than this is not worth a partial
+
 // Everything the tile schedule depends on (shared by plan creation and the host-side dump).
-static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p) {
+static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, int cta_mt, GemmParams& p) {
   const int bn_out = (d.epi == EPI_SWIGLU) ? d.bn / 2 : d.bn;
   p.M = d.M; p.N = d.N; p.K = d.K;
   p.m_tiles = (d.M + BM - 1) / BM;
@@ -121,8 +135,19 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p
   p.op = d.op; p.epi = d.epi; p.sched = d.sched;
   p.m_per_rank = d.m_per_rank > 0 ? d.m_per_rank : d.M;
   p.cta_m = cta_m;
-  p.unit_m = (p.m_tiles + p.cta_m - 1) / p.cta_m;
-  p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? (p.m_tiles / d.R) / p.cta_m : p.unit_m;
+  p.cta_mt = cta_mt;
+  p.sub_tiles = cta_m * cta_mt;
+  p.unit_m = (p.m_tiles + p.sub_tiles - 1) / p.sub_tiles;
+  p.seg_m_tiles = (d.sched == SCHED_SEGMENT) ? (p.m_tiles / d.R) / p.sub_tiles : p.unit_m;
+  // row units walked together: their A rows (unit rows x K) should stay in L2 while the B column
+  // blocks stream past, and a wave of workers should still span several column blocks
+  {
+    const int64_t unit_bytes = static_cast<int64_t>(p.sub_tiles) * BM * d.K * 2;
+    int g = d.raster_g > 0 ? d.raster_g : static_cast<int>((48ll << 20) / (unit_bytes > 0 ? unit_bytes : 1));
+    if (g < 1) g = 1;
+    if (g > 16) g = 16;
+    p.raster_g = g;
+  }
   if (d.sched == SCHED_SEGMENT && (p.m_tiles % d.R != 0 || p.m_per_rank % BM != 0))
     throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
   for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
@@ -135,7 +160,7 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p
   p.skip_comm = d.skip_comm;
   p.push_ctas = d.push_ctas;
   p.push_skip_rounds = d.push_skip_rounds;
-  const int own_tickets = p.unit_m * p.cta_m * p.n_tiles;
+  const int own_tickets = p.unit_m * p.sub_tiles * p.n_tiles;
   if (d.ticket_stride > 0 && d.ticket_stride < own_tickets)
     throw std::runtime_error("tridist_b200: ticket stride " + std::to_string(d.ticket_stride) +
                              " is smaller than this call's " + std::to_string(own_tickets) + " tile tickets");
@@ -145,34 +170,111 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, GemmParams& p
   p.ag_flag_stride = d.ag_flag_stride > 0 ? d.ag_flag_stride : p.n_chunks;
 }
 
-// Persistent grid: one CTA (or CTA pair) per scheduling position, at most one per SM.
-static int grid_for(const GemmParams& p, int max_ctas, int sms) {
+// Persistent grid: one CTA (or CTA pair) per scheduling position, at most one per SM; and the
+// split of the last, partial round along K (fills p.sk_tiles / p.sk_slices).
+static int grid_for(const GemmPlanDesc& d, GemmParams& p, int max_ctas, int sms) {
   const int positions = sched_positions(p);
   int g = max_ctas > 0 ? max_ctas : sms;
   if (g > sms) g = sms;
-  g /= p.cta_m;                             // units that can run at once
-  int units = positions < g ? positions : g;
-  if (units < 1) units = 1;
-  return units * p.cta_m;
+  g /= p.cta_m;                             // workers that can run at once
+  if (g < 1) g = 1;
+  p.sk_tiles = 0;
+  p.sk_slices = 1;
+  const bool may_split = d.allow_splitk && d.sched != SCHED_LIST && d.probe == 0 && positions > 0;
+  int slices_cap = p.k_blocks / kMinKBlocksPerSlice;
+  if (slices_cap > kMaxSlices) slices_cap = kMaxSlices;
+  int workers;
+  if (positions < g) {
+    // fewer tiles than workers (skinny M): every tile is cut
+    int s = may_split ? g / positions : 1;
+    if (s > slices_cap) s = slices_cap;
+    if (s >= 2) {
+      p.sk_tiles = positions;
+      p.sk_slices = s;
+      workers = positions * s;
+    } else {
+      workers = positions < 1 ? 1 : positions;
+    }
+  } else {
+    workers = g;
+    int pushers = 0, skip = 0;
+    if (d.op == OP_AG && d.R > 1 && !d.skip_comm && d.push_ctas > 0 && d.push_ctas < workers * p.cta_m) {
+      pushers = (d.push_ctas + p.cta_m - 1) / p.cta_m;
+      skip = d.push_skip_rounds;
+    }
+    const int r = remainder_positions(positions, workers, pushers, skip);
+    int s = (may_split && r > 0) ? workers / r : 1;
+    if (s > slices_cap) s = slices_cap;
+    if (s >= 2) {
+      p.sk_tiles = r;
+      p.sk_slices = s;
+    }
+  }
+  return workers * p.cta_m;
 }
+
+// Scratch for the split-K partials: one slot per CTA of a launch (two fp32 accumulators of
+// 128 x 256) and one epoch word per slot; allocated once per device, on first use, never freed.
+constexpr int kSkSlots = 160;
+constexpr int64_t kSkSlotWords = 2ll * BM * 256;
+struct SkScratch {
+  float* ws = nullptr;
+  uint32_t* flags = nullptr;
+};
+static SkScratch& sk_scratch() {
+  static SkScratch per_dev[64];
+  int dev = 0;
+  check(cudaGetDevice(&dev), "cudaGetDevice");
+  SkScratch& s = per_dev[dev & 63];
+  if (s.ws == nullptr) {
+    check(cudaMalloc(&s.ws, kSkSlots * kSkSlotWords * sizeof(float)), "cudaMalloc(split-K scratch)");
+    check(cudaMalloc(&s.flags, kSkSlots * sizeof(uint32_t)), "cudaMalloc(split-K flags)");
+    check(cudaMemset(s.flags, 0, kSkSlots * sizeof(uint32_t)), "cudaMemset(split-K flags)");
+  }
+  return s;
+}
+static uint32_t g_sk_epoch = 0;
 
 std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d, int sms) {
   if (d.sched == SCHED_LIST) throw std::runtime_error("tridist_b200: a tile list is its own schedule");
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   const int cta_m = choose_cta_m(d);
-  fill_schedule_fields(d, cta_m, p);
-  const int grid_x = grid_for(p, d.max_ctas, sms);
+  fill_schedule_fields(d, cta_m, choose_cta_mt(d, cta_m), p);
+  const int grid_x = grid_for(d, p, d.max_ctas, sms);
   const WorkerSchedule ws = make_worker_schedule(p, grid_x, cta_m);
-  const int positions = sched_positions(p);
   std::vector<std::vector<std::array<int, 5>>> out(grid_x);
   for (int cta = 0; cta < grid_x; ++cta) {
     const int sub = cta % cta_m, worker = cta / cta_m;
-    for (int i = 0, pos = ws.pos_of(worker, 0); pos < positions; pos = ws.pos_of(worker, ++i)) {
-      const TileCoord t = tile_at(p, p.seg_order, pos, sub);
+    WorkIter wit;
+    WorkItem wi;
+    while (wit.next(ws, worker, p.k_blocks, wi)) {
+      const TileCoord t = tile_at(p, p.seg_order, wi.pos, sub);
       if (!t.valid) continue;
-      out[cta].push_back({t.m_tile, t.n_tile, t.linear, t.owner_key, pos});
+      // a tile cut along K appears once, with the worker that finishes it (slice 0)
+      if (wi.slice > 0) continue;
+      for (int h = 0; h < p.cta_mt; ++h)
+        out[cta].push_back({t.m_tile + h, t.n_tile, tile_linear(p, t, h), t.owner_key, wi.pos});
     }
+  }
+  return out;
+}
+
+// The K ranges of the tiles that are cut along K: {scheduling position, first CTA of the worker,
+// slice, slices, first k-block, end k-block} for every worker that takes part.
+std::vector<std::array<int, 6>> splitk_dump(const GemmPlanDesc& d, int sms) {
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const int cta_m = choose_cta_m(d);
+  fill_schedule_fields(d, cta_m, choose_cta_mt(d, cta_m), p);
+  const int grid_x = grid_for(d, p, d.max_ctas, sms);
+  const WorkerSchedule ws = make_worker_schedule(p, grid_x, cta_m);
+  std::vector<std::array<int, 6>> out;
+  for (int worker = 0; worker < grid_x / cta_m; ++worker) {
+    WorkIter wit;
+    WorkItem wi;
+    while (wit.next(ws, worker, p.k_blocks, wi))
+      if (wi.slices > 1) out.push_back({wi.pos, worker * cta_m, wi.slice, wi.slices, wi.kb0, wi.kb1});
   }
   return out;
 }
@@ -189,7 +291,7 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
   std::memset(&p, 0, sizeof(p));
   const int cta_m = choose_cta_m(d);
   try {
-    fill_schedule_fields(d, cta_m, p);
+    fill_schedule_fields(d, cta_m, choose_cta_mt(d, cta_m), p);
   } catch (const std::exception& ex) {
     bad.push_back(ex.what());
     return bad;
@@ -197,16 +299,16 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
   const bool multi = d.R > 1;
   // ---- tiles and tickets: every tile once, ticket indices unique and inside the ticket planes ----
   const int64_t tickets = (d.sched == SCHED_STRIDED)
-      ? static_cast<int64_t>(p.unit_m) * p.cta_m * p.n_tiles
+      ? static_cast<int64_t>(p.unit_m) * p.sub_tiles * p.n_tiles
       : static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const auto sched = schedule_dump(d, sms);
-  std::vector<char> seen(static_cast<size_t>(p.unit_m) * p.cta_m * p.n_tiles, 0);
+  std::vector<char> seen(static_cast<size_t>(p.unit_m) * p.sub_tiles * p.n_tiles, 0);
   std::vector<char> ticket_used(static_cast<size_t>(tickets > 0 ? tickets : 1), 0);
   int64_t real_tiles = 0;
   for (const auto& cta : sched) {
     for (const auto& t : cta) {
       const int mt = t[0], nt = t[1], lin = t[2];
-      if (mt < 0 || mt >= p.unit_m * p.cta_m || nt < 0 || nt >= p.n_tiles) {
+      if (mt < 0 || mt >= p.unit_m * p.sub_tiles || nt < 0 || nt >= p.n_tiles) {
         bad.push_back("tile (" + std::to_string(mt) + ", " + std::to_string(nt) + ") outside the tile grid");
         continue;
       }
@@ -282,15 +384,22 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
   plan->bn = d.bn;
   plan->bf16 = d.bf16;
   plan->cta_m = choose_cta_m(d);
+  plan->cta_mt = choose_cta_mt(d, plan->cta_m);
   for (int par = 0; par < 2; ++par) {
     GemmParams& p = plan->prm[par];
     std::memset(&p, 0, sizeof(p));
-    fill_schedule_fields(d, plan->cta_m, p);
+    fill_schedule_fields(d, plan->cta_m, plan->cta_mt, p);
     p.order_table = reinterpret_cast<const int32_t*>(d.order_table);
     p.tile_list = reinterpret_cast<const int32_t*>(d.tile_list);
     p.is_bf16 = d.bf16 ? 1 : 0;
     p.c = reinterpret_cast<void*>(d.c);
     p.ldc = d.ldc;
+    // tiles that stay on this GPU leave through staged TMA stores when c can carry a tensor map
+    p.c_tma = 0;
+    if (d.c != 0 && d.c % 16 == 0 && (d.ldc * 2) % 16 == 0 && (d.R == 1 || d.op == OP_PLAIN || d.op == OP_AG)) {
+      p.tma_c = make_tmap(reinterpret_cast<void*>(d.c), d.M, d.N, d.ldc, d.bf16);
+      p.c_tma = 1;
+    }
     p.tma_a = make_tmap(reinterpret_cast<void*>(d.a), d.a_rows, d.K, d.lda, d.bf16);
     p.tma_b = make_tmap(reinterpret_cast<void*>(d.b), d.b_rows, d.K, d.ldb, d.bf16);
     p.tma_a_ws = p.tma_a;
@@ -332,7 +441,18 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.probe = (d.op == OP_PLAIN && d.R == 1) ? d.probe : 0;
     p.env.rank = static_cast<uint32_t>(d.rank);
   }
-  plan->grid_x = grid_for(plan->prm[0], d.max_ctas, num_sms());
+  plan->grid_x = grid_for(d, plan->prm[0], d.max_ctas, num_sms());
+  plan->prm[1].sk_tiles = plan->prm[0].sk_tiles;
+  plan->prm[1].sk_slices = plan->prm[0].sk_slices;
+  if (plan->prm[0].sk_tiles > 0) {
+    if (plan->grid_x > kSkSlots) throw std::runtime_error("tridist_b200: split-K scratch has too few slots");
+    const SkScratch& sc = sk_scratch();
+    for (int par = 0; par < 2; ++par) {
+      plan->prm[par].sk_ws = sc.ws;
+      plan->prm[par].sk_flags = sc.flags;
+      plan->prm[par].sk_slot_words = plan->cta_mt * BM * plan->bn;
+    }
+  }
   std::lock_guard<std::mutex> lk(g_mu);
   const int64_t id = g_next_plan++;
   g_plans[id] = plan;
@@ -355,13 +475,13 @@ static GemmPlan* find_plan(int64_t id) {
   return it->second;
 }
 
-template <int BN, bool kBf16, int kCtaM, bool kStaging>
+template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
 static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
-  set_attr_once<BN, kBf16, kCtaM, kStaging>();
+  set_attr_once<BN, kBf16, kCtaM, kStaging, kMT>();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid_x, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = TileShape<BN, kCtaM, kStaging>::kSmemBytes;
+  cfg.dynamicSmemBytes = TileShape<BN, kCtaM, kStaging, kMT>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -371,7 +491,7 @@ static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const GemmParams* none = nullptr;
-  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM, kStaging>, p, none),
+  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM, kStaging, kMT>, p, none),
         "fused_gemm_kernel launch");
 }
 
@@ -384,21 +504,29 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
   p.order_table = reinterpret_cast<const int32_t*>(order_table);
   p.skip_comm = skip_comm & 1;
   p.comm_only = (skip_comm >> 1) & 1;
+  p.sk_epoch = ++g_sk_epoch;
   // operators that ship data to other ranks (epilogue tiles, all-gather push) need the staging area
   const bool staging = p.R > 1 && (p.op == OP_RS || p.op == OP_AR1 || p.op == OP_AR2 || p.op == OP_AG);
 #define TDB_LAUNCH(BN_, PAIR_)                                                              \
   do {                                                                                      \
     if (plan->bf16) {                                                                       \
-      if (staging) launch_one<BN_, true, PAIR_, true>(p, plan->grid_x, stream);             \
-      else launch_one<BN_, true, PAIR_, false>(p, plan->grid_x, stream);                    \
+      if (staging) launch_one<BN_, true, PAIR_, true, 1>(p, plan->grid_x, stream);          \
+      else launch_one<BN_, true, PAIR_, false, 1>(p, plan->grid_x, stream);                 \
     } else {                                                                                \
-      if (staging) launch_one<BN_, false, PAIR_, true>(p, plan->grid_x, stream);            \
-      else launch_one<BN_, false, PAIR_, false>(p, plan->grid_x, stream);                   \
+      if (staging) launch_one<BN_, false, PAIR_, true, 1>(p, plan->grid_x, stream);         \
+      else launch_one<BN_, false, PAIR_, false, 1>(p, plan->grid_x, stream);                \
     }                                                                                       \
   } while (0)
   if (plan->bn == 256) {
-    if (plan->cta_m == 2) TDB_LAUNCH(256, 2);
-    else TDB_LAUNCH(256, 1);
+    if (plan->cta_m == 2 && plan->cta_mt == 2) {
+      // 256 rows per CTA: the ring has four stages and the staging area is always there
+      if (plan->bf16) launch_one<256, true, 2, true, 2>(p, plan->grid_x, stream);
+      else launch_one<256, false, 2, true, 2>(p, plan->grid_x, stream);
+    } else if (plan->cta_m == 2) {
+      TDB_LAUNCH(256, 2);
+    } else {
+      TDB_LAUNCH(256, 1);
+    }
   } else {
     TDB_LAUNCH(128, 1);
   }
@@ -408,15 +536,15 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
 
 template <int BN, bool kBf16>
 static void launch_emulated(const GemmParams* dev, int grid_x, int vranks, cudaStream_t stream) {
-  set_attr_once<BN, kBf16, 1, true>();
+  set_attr_once<BN, kBf16, 1, true, 1>();
   GemmParams dummy;
   std::memset(&dummy, 0, sizeof(dummy));
   void* args[2] = {&dummy, &dev};
   // Cooperative launch: the runtime refuses the launch unless every CTA of
   // every emulated rank can be resident at once, which the cross-rank waits need.
-  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1, true>),
+  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1, true, 1>),
                                     dim3(grid_x, vranks, 1), dim3(kThreads, 1, 1), args,
-                                    TileShape<BN, 1, true>::kSmemBytes, stream),
+                                    TileShape<BN, 1, true, 1>::kSmemBytes, stream),
         "fused_gemm_kernel cooperative launch");
 }
 
@@ -437,7 +565,15 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
     host[i] = pl->prm[parity & 1];
     host[i].round = round;
     host[i].skip_comm = skip_comm;
+    host[i].sk_epoch = g_sk_epoch + 1;
     if (pl->grid_x < grid_x) grid_x = pl->grid_x;
+  }
+  // the K split was laid out for each plan's own grid: a launch on a smaller grid deals whole tiles
+  for (int i = 0; i < vr; ++i) {
+    if (find_plan(ids[i])->grid_x != grid_x) {
+      host[i].sk_tiles = 0;
+      host[i].sk_slices = 1;
+    }
   }
   if (!first->dev_params)
     check(cudaMalloc(&first->dev_params, sizeof(GemmParams) * kMaxRanks), "cudaMalloc(params)");
@@ -452,6 +588,7 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
     if (first->bf16) launch_emulated<128, true>(first->dev_params, grid_x, vr, stream);
     else launch_emulated<128, false>(first->dev_params, grid_x, vr, stream);
   }
+  ++g_sk_epoch;
   ++g_launches;
 }
 

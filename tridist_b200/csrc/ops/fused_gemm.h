@@ -36,6 +36,9 @@ struct GemmPlanDesc {
   int swiglu_up_row0 = 0;
   int max_ctas = 0;
   int allow_pair = 1;   // let 256-wide tiles run on CTA pairs (cluster of 2, cta_group::2 MMA)
+  int allow_wide = 1;   // let CTA pairs take 512 x 256 tiles (256 rows per CTA) where the rows allow
+  int allow_splitk = 1; // let the tiles of the last, partial scheduling round be cut along K
+  int raster_g = 0;     // row units walked together (0 = sized so that their A rows stay in L2)
   // all-gather
   int64_t peer_ws[2][8] = {};
   int64_t peer_ag_flags[8] = {};
@@ -82,6 +85,9 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
 // needed): for every CTA of the grid the tiles it would process, in order, as
 // {m_tile, n_tile, ticket index, owner key, scheduling position}. `sms` = SMs of the target GPU.
 std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d, int sms);
+
+// The tiles cut along K: {position, first CTA of the worker, slice, slices, first k-block, end k-block}.
+std::vector<std::array<int, 6>> splitk_dump(const GemmPlanDesc& d, int sms);
 
 // Sizes of the buffers a plan will touch (0 = not given, that check is skipped).
 struct PlanExtents {

@@ -128,7 +128,11 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              M=M, N=N, K=K, a=a.data_ptr(), a_rows=a.shape[0], lda=a.stride(0),
              b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
              status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
-             max_ctas=env_int("TRIDIST_MAX_CTAS", 0), poll_ns=env_int("TRIDIST_POLL_NS", 0),
+             max_ctas=env_int("TRIDIST_MAX_CTAS", 0) or
+             (NUM_SMS_HINT // world.num_ranks if getattr(world, "kind", "") == "emulated" else 0),
+             poll_ns=env_int("TRIDIST_POLL_NS", 0),
+             allow_wide=env_int("TRIDIST_WIDE", 1), allow_splitk=env_int("TRIDIST_SPLITK", 1),
+             raster_g=env_int("TRIDIST_RASTER_G", 0),
              prof=(prof_buffer().data_ptr() if prof_buffer() is not None else 0),
              allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and getattr(world, "kind", "") != "emulated") else 0)
     return d
