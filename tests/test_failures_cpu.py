@@ -105,3 +105,40 @@ def test_heartbeat_finds_silent_peer():
     assert b0.stale_peers(0.2) == []
     time.sleep(0.3)
     assert b0.stale_peers(0.2) == [1]                 # no beat since the last look
+
+
+def _multicast_one_rank_cannot(rank, R, outdir):
+    """ProcessWorld.alloc_multicast with a stand-in allocator that fails on rank 1: every rank must
+    come back with None (and the reason), none may enter the allocator's rendezvous."""
+    from tridist_b200.parallel import runtime
+
+    class FakeSymm:
+        rendezvous_calls = 0
+
+        @staticmethod
+        def empty(n, dtype=None, device=None):
+            if rank == 1:
+                raise RuntimeError("no multicast on this rank")
+            return torch.empty(n, dtype=torch.uint8)
+
+        @staticmethod
+        def rendezvous(t, group):
+            FakeSymm.rendezvous_calls += 1
+            raise AssertionError("rendezvous entered although a rank could not allocate")
+
+    runtime._symm_mem_module = lambda: FakeSymm
+    w = runtime.ProcessWorld.__new__(runtime.ProcessWorld)      # host logic only: no device, no heap
+    runtime._WorldBase.__init__(w)
+    w.rank, w.num_ranks, w.group, w.device = rank, R, None, 0
+    got = runtime.ProcessWorld.alloc_multicast(w, 4096)
+    with open(os.path.join(outdir, f"rank{rank}.txt"), "w") as fh:
+        fh.write(f"{got is None}|{FakeSymm.rendezvous_calls}|{getattr(w, 'multicast_unavailable', '')}")
+
+
+def test_multicast_allocation_fails_on_all_ranks_together():
+    with tempfile.TemporaryDirectory() as d:
+        spawn(_multicast_one_rank_cannot, 2, args=(d,), timeout=60)
+        for r in range(2):
+            none, calls, why = open(os.path.join(d, f"rank{r}.txt")).read().split("|", 2)
+            assert none == "True" and calls == "0"
+            assert "rank 1" in why and "no multicast on this rank" in why

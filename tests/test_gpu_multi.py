@@ -219,3 +219,52 @@ def _nvls_all_reduce(rank, R):
 def test_nvls_all_reduce(R):
     from tridist_b200.utils.testing import spawn
     spawn(_nvls_all_reduce, R, backend="nccl", timeout=300)
+
+
+def _nvls_reduce_scatter(rank, R):
+    """GEMM + reduce-scatter with the sum done by the NVSwitch (multimem.ld_reduce by the owner's
+    communication warps). As above, errors are raised only after the collective release."""
+    from tridist_b200.ops import create_gemm_rs_intra_node_context, gemm_rs_intra_node
+    from tridist_b200.ops.gemm_reduce_scatter import finalize_gemm_rs_context, pick_mode
+    from tridist_b200.parallel.runtime import init_runtime
+    from tridist_b200.utils.testing import ks_inputs
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    w = init_runtime(rank, R)
+    dt = torch.bfloat16
+    max_M, N, kl = 512 * R, 768, 1024
+    rs = create_gemm_rs_intra_node_context(max_M, N, dt, rank, R, nvls=True)
+    if rs.mc is None:
+        if rank == 0:
+            print("NVLS unavailable:", getattr(w, "multicast_unavailable", "?"), flush=True)
+        finalize_gemm_rs_context(rs)
+        return
+    problems = []
+    try:
+        rs.mode = "nvls"
+        assert pick_mode(rs, max_M) == "nvls"
+        for it, M in enumerate([max_M, max_M, max_M // 2, max_M // 4, max_M, max_M // 2]):
+            a_all, b_all = ks_inputs(R, M, N, kl, 40 + it, dt)
+            ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
+            out = gemm_rs_intra_node(a_all[rank].cuda(), b_all[rank].cuda(), rs)
+            torch.cuda.synchronize()
+            w.check()
+            mp_ = M // R
+            err = (out.float() - ref[rank * mp_:(rank + 1) * mp_]).abs().max().item()
+            if not err < 6e-2:
+                problems.append(f"round {it} M={M}: max error {err}")
+    except Exception as exc:                              # reported after the collective release
+        problems.append(f"{type(exc).__name__}: {exc}")
+    finally:
+        try:
+            finalize_gemm_rs_context(rs)
+        except Exception as exc:
+            problems.append(f"release failed: {exc}")
+    if rank == 0:
+        print("NVLS reduce-scatter:", "ok" if not problems else problems, flush=True)
+    assert not problems, problems
+
+
+@pytest.mark.parametrize("R", [2, pytest.param(4, marks=_need(4)), pytest.param(8, marks=_need(8))])
+def test_nvls_reduce_scatter(R):
+    from tridist_b200.utils.testing import spawn
+    spawn(_nvls_reduce_scatter, R, backend="nccl", timeout=300)

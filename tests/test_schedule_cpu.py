@@ -135,3 +135,22 @@ def test_reduce_scatter_walks_own_segment_last():
         owners = [t[0] // rows_per_seg for t in cta]
         assert owners[-1] == rank or rank not in owners
         assert [order.index(o) for o in owners] == sorted(order.index(o) for o in owners)
+
+
+@pytest.mark.parametrize("R", [4, 8])
+def test_reduce_scatter_through_the_switch_walks_owners_in_lockstep(R):
+    """Same order on every rank: position i is tile i // R of owner i % R, so the R partials of a tile
+    are produced at about the same time everywhere and the owner can sum them right away."""
+    M, N = 8192, 12288
+    dumps = []
+    for rank in (0, R - 1):
+        out = _dump(op=OP_RS, sched=SCHED_SEGMENT, M=M, N=N, bn=256, R=R, rank=rank, m_per_rank=M // R,
+                    seg_order=list(range(R)), seg_interleave=1, nvls=1, slot_stride=0)
+        dumps.append(out)
+        seen = [(t[0], t[1]) for cta in out for t in cta]
+        assert len(seen) == len(set(seen)) and set(seen) == _tiles(M, N, 256)
+    assert dumps[0] == dumps[1]
+    rows_per_seg = (M // R) // BM
+    by_pos = sorted({(t[4], t[0] // rows_per_seg) for cta in dumps[0] for t in cta})
+    owners = [o for _, o in by_pos]
+    assert owners[:2 * R] == list(range(R)) * 2

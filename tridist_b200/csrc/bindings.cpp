@@ -62,6 +62,7 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   }
   g.order_table = get<int64_t>(d, "order_table", 0);
   g.strided_interleave = get<int>(d, "strided_interleave", 0);
+  g.seg_interleave = get<int>(d, "seg_interleave", 0);
   g.tile_list = get<int64_t>(d, "tile_list", 0);
   g.list_len = get<int>(d, "list_len", 0);
   g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);

@@ -10,7 +10,10 @@
 //                                           the epilogue stores partial tiles straight into
 //                                           the owner rank's per-source slot; tiles of the
 //                                           rank's own rows are reduced in the epilogue
-//                                           (fp32) from the slots the peers filled
+//                                           (fp32) from the slots the peers filled; or, through
+//                                           the switch: partial tiles stay in the producer's own
+//                                           multicast-bound plane and the owner's communication
+//                                           warps read their sum with multimem.ld_reduce
 //   OP_AR1     one-shot all-reduce: every partial tile goes to all peers, each rank reduces
 //   OP_AR2     two-shot all-reduce: every partial tile goes to the tile's owner; the owner's
 //              communication warps reduce it and broadcast the result to all ranks
@@ -139,7 +142,7 @@ struct alignas(64) GemmParams {
   CUtensorMap tma_a;       // A [rows, K]; for OP_AG this rank's local shard [M_pr, K]
   CUtensorMap tma_a_ws;    // OP_AG: gathered workspace [M, K] (this round's parity)
   CUtensorMap tma_b;       // B [N_rows, K], box 128 rows
-  CUtensorMap tma_c;       // local output (store map, box 128 rows x 64 columns), valid if c_tma
+  CUtensorMap tma_c32;     // local output (store map, box 32 rows x 64 columns), valid if c_tma
   // Store maps (box 128 rows x 64 columns, 128-byte swizzle) over this rank's slot inside
   // every rank's slot buffer.
   CUtensorMap tma_slot[kMaxRanks];
@@ -156,6 +159,7 @@ struct alignas(64) GemmParams {
   int32_t raster_g;        // units along M walked together (L2 residency of their A rows)
   int32_t seg_order[kMaxRanks];
   int32_t strided_interleave;  // SCHED_STRIDED: same unit order on every rank (see tile_at)
+  int32_t seg_interleave;      // SCHED_SEGMENT: position i is tile i / R of segment order[i % R]
   const int32_t* order_table;  // optional device table overriding seg_order (R entries)
   const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
   int32_t list_len;
@@ -166,7 +170,7 @@ struct alignas(64) GemmParams {
 
   void* c;                 // local output (see per-op meaning in the kernel)
   int64_t ldc;
-  int32_t c_tma;           // tma_c is valid: local tiles leave through staged TMA stores
+  int32_t c_tma;           // tma_c32 is valid: local tiles leave through staged TMA stores
 
   // ---- split-K of the remainder round ----
   int32_t sk_tiles;        // scheduling positions (the last ones) that are cut along K
@@ -198,6 +202,8 @@ struct alignas(64) GemmParams {
   // OP_AR2 through the switch: partials stay in this rank's own buffer (peer_slots[*] all name
   // it, slot_stride = 0); the owner of a tile sums the R copies with multimem.ld_reduce on
   // mc_part and writes the result into every rank's result buffer with multimem.st on mc_res.
+  // OP_RS through the switch: the same, except that the owner of a tile is the rank that keeps
+  // its rows and the sum is stored into that rank's c only.
   int32_t nvls;
   void* mc_part;                   // multicast address of the partial buffer [M][N] (this parity)
   void* mc_res;                    // multicast address of the result buffer [M][N] (this parity)
@@ -253,8 +259,10 @@ __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const
   int um = 0, nt = 0, ulin = -1;
   if (p.sched == SCHED_SEGMENT) {
     const int per_seg = p.seg_m_tiles * p.n_tiles;
-    const int si = pos / per_seg;
-    const int u = pos - si * per_seg;
+    // interleaved: every rank walks the segments in lockstep (tile k of every owner, then tile
+    // k + 1 ...), so that all partials of a tile exist at about the same time on all ranks
+    const int si = p.seg_interleave ? pos % p.R : pos / per_seg;
+    const int u = p.seg_interleave ? pos / p.R : pos - si * per_seg;
     raster_grouped(u, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
     um += order[si] * p.seg_m_tiles;
   } else if (p.sched == SCHED_STRIDED) {
@@ -997,7 +1005,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // a CTA tile's later blocks can fall past the last row block
       const bool tile_has_rows = m_tile * BM < p.M;
       if (multi && tile_has_rows) {
-        if (p.op == OP_RS) {
+        if (p.op == OP_RS && p.nvls) {
+          // through the switch: every partial (own included) stays in this rank's own plane; the
+          // communication warps of the rank that keeps the rows read the sum, no epilogue waits
+          owner = min((m_tile * BM) / p.m_per_rank, p.R - 1);
+          o_lo = o_hi = owner;
+          tile_reduces = false;
+          tile_publishes = true;
+        } else if (p.op == OP_RS) {
           owner = min(row / p.m_per_rank, p.R - 1);
           o_lo = (m_tile * BM) / p.m_per_rank;
           o_hi = min((min(m_tile * BM + BM, p.M) - 1) / p.m_per_rank, p.R - 1);
@@ -1029,11 +1044,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           // at a time in TMA layout and let one thread ship them with 2-D tiled stores
           // (two 128 x 64 boxes per destination) -- few large copy-engine operations.
           const int dest = (p.op == OP_RS) ? o_lo : owner;      // uniform over the CTA
-          const int row0 = (p.op == OP_RS) ? m_tile * BM - dest * p.m_per_rank : m_tile * BM;
+          // peer slots hold the owner's rows only; a plane read through the switch holds all rows
+          const int row0 = (p.op == OP_RS && !p.nvls) ? m_tile * BM - dest * p.m_per_rank : m_tile * BM;
           for (int half = 0; half < BN / kStageCols; ++half) {
             const int col0 = t.n_tile * BN + half * kStageCols;
             if (col0 >= p.N) break;
-            if (etid == 0) tma_store_wait_read<0>();   // earlier stores have read the staging
+            if (lane == 0) tma_store_wait_read<0>();   // earlier stores have read the staging
             named_bar_sync(2, kEpiThreads);
 #pragma unroll 1
             for (int c = 0; c < kStageCols / 32; ++c) {
@@ -1118,7 +1134,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         named_bar_sync(2, kEpiThreads);
         if (p.op == OP_RS) {
           const int o = o_lo + etid;
-          if (o <= o_hi && o != p.rank)
+          if (o <= o_hi && (o != p.rank || p.nvls))
             st_release_sys(p.peer_tile_flags[o] + p.rank * tiles + lin, p.round);
         } else if (p.op == OP_AR1) {
           if (etid < p.R && etid != p.rank)
@@ -1160,53 +1176,67 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         uint8_t* const c_base = reinterpret_cast<uint8_t*>(p.c);
         const bool local_tile = !multi || op == OP_PLAIN || op == OP_AG;
         if (local_tile && staging_free && p.c_tma) {
-          // Local result: convert 64 columns at a time into one of two swizzled 128 x 64 boxes
-          // and let one thread ship the box with a 2-D tiled store (rows and columns past the
-          // end of c are clipped by the copy engine). The accumulator is free as soon as its
-          // last columns are in shared memory; nobody waits for the stores here.
+          // Local result: every epilogue warp converts its 32 rows, 64 columns at a time, into
+          // one of its two swizzled 32 x 64 boxes and ships the box with a 2-D tiled store of its
+          // own (rows and columns past the end of c are clipped by the copy engine). The four
+          // warps never meet at a barrier here, and the accumulator is free as soon as its last
+          // columns are in shared memory; nobody waits for the stores.
           const int out_col0 = swiglu ? t.n_tile * (BN / 2) : t.n_tile * BN;
-          const int boxes = swiglu ? BN / 128 : BN / 64;
-#pragma unroll 1
-          for (int j = 0; j < boxes; ++j) {
+          constexpr int kWarpBox = 32 * 128;
+          uint8_t* const wbox = staging + q * (2 * kWarpBox);
+          const int out_row0 = m_tile * BM + q * 32;
+          uint32_t ra[32], rb[32];           // accumulator columns in flight (plain store only)
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) {
+            if (swiglu && j >= BN / 128) break;
             const int ocol = out_col0 + j * 64;
             if (ocol >= n_cols) break;
-            uint8_t* box = staging + (j & 1) * kBoxBytes;
-            // the store that last read this box was issued two groups ago (any group for j = 0)
-            if (etid == 0) {
-              if (j == 0) tma_store_wait_read<0>();
-              else tma_store_wait_read<1>();
-            }
-            named_bar_sync(2, kEpiThreads);
+            uint8_t* box = wbox + (j & 1) * kWarpBox;
+            uint32_t pk[32];                 // 64 columns of this lane's row, packed to 16 bit
             if (swiglu) {
               // gate in accumulator columns [0, BN/2), up in [BN/2, BN)
-#pragma unroll 1
+#pragma unroll
               for (int cc = 0; cc < 2; ++cc) {
                 uint32_t g[32], u[32];
                 tmem_ld_32x32b_x32(taddr + j * 64 + cc * 32, g);
                 tmem_ld_32x32b_x32(taddr + BN / 2 + j * 64 + cc * 32, u);
                 tmem_ld_wait();
-                float acc[32];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) acc[e] = silu(__uint_as_float(g[e])) * __uint_as_float(u[e]);
-                stage_row32_swizzled<kBf16>(box, r_in_tile, cc, acc);
+                for (int e = 0; e < 16; ++e)
+                  pk[cc * 16 + e] = pack2<kBf16>(silu(__uint_as_float(g[2 * e])) * __uint_as_float(u[2 * e]),
+                                                 silu(__uint_as_float(g[2 * e + 1])) * __uint_as_float(u[2 * e + 1]));
               }
             } else {
-              uint32_t r0[32], r1[32];
-              tmem_ld_32x32b_x32(taddr + j * 64, r0);
-              tmem_ld_32x32b_x32(taddr + j * 64 + 32, r1);
+              // the loads of box j were issued while box j - 1 was being staged
+              if (j == 0) {
+                tmem_ld_32x32b_x32(taddr, ra);
+                tmem_ld_32x32b_x32(taddr + 32, rb);
+              }
               tmem_ld_wait();
-              float acc[32];
 #pragma unroll
-              for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r0[e]);
-              stage_row32_swizzled<kBf16>(box, r_in_tile, 0, acc);
-#pragma unroll
-              for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r1[e]);
-              stage_row32_swizzled<kBf16>(box, r_in_tile, 1, acc);
+              for (int e = 0; e < 16; ++e) {
+                pk[e] = pack2<kBf16>(__uint_as_float(ra[2 * e]), __uint_as_float(ra[2 * e + 1]));
+                pk[16 + e] = pack2<kBf16>(__uint_as_float(rb[2 * e]), __uint_as_float(rb[2 * e + 1]));
+              }
+              if (j + 1 < BN / 64 && out_col0 + (j + 1) * 64 < n_cols) {
+                tmem_ld_32x32b_x32(taddr + (j + 1) * 64, ra);
+                tmem_ld_32x32b_x32(taddr + (j + 1) * 64 + 32, rb);
+              }
             }
+            // the store that last read this box was issued two groups ago (any group for j = 0)
+            if (lane == 0) {
+              if (j == 0) tma_store_wait_read<0>();
+              else tma_store_wait_read<1>();
+            }
+            __syncwarp();
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(box + lane * 128 + ((v ^ (lane & 7)) * 16)) =
+                  make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
             fence_proxy_async_smem();
-            named_bar_sync(2, kEpiThreads);
-            if (etid == 0) {
-              tma_store_2d(&p.tma_c, box, ocol, m_tile * BM);
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&p.tma_c32, box, ocol, out_row0);
               tma_store_commit();
             }
           }
@@ -1274,7 +1304,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       ++it;
     }
     // staged stores must have read shared memory before the CTA goes away
-    if (kStaging && etid == 0) tma_store_wait_all<0>();
+    if (kStaging && lane == 0) tma_store_wait_all<0>();
     if (prof && etid == 0) {
       prof[PROF_EPI_BUSY] = acc_busy;
       prof[PROF_EPI_PUBLISH] = acc_pub;
@@ -1354,6 +1384,77 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         // every copy of this thread has completed: the staging area now belongs to the epilogue
         __threadfence_block();
         s_flags[2] = 1;
+      }
+    } else if (p.op == OP_RS && p.nvls && p.R > 1) {
+      // Reduce-scatter through the switch: the 128-row blocks of this rank's own rows, in the
+      // order all ranks compute them, spread over the CTAs. Wait for the R partial tickets of a
+      // block, read the SUM of the R ranks' partials with multimem.ld_reduce (added inside the
+      // switch, fp32 accumulation) and store it into c.
+      const int per_seg = p.seg_m_tiles * p.n_tiles;
+      bool ok = true;
+      int owned_seq = 0;
+      const bool cprof = prof && ctid == 0;
+      uint64_t acc_aw = 0, acc_ak = 0;
+      uint8_t* const mc_in = reinterpret_cast<uint8_t*>(p.mc_part);
+      for (int u = 0; ok && u < per_seg; ++u) {
+        int um, nt;
+        raster_grouped(u, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
+        for (int subt = 0; ok && subt < p.sub_tiles; ++subt, ++owned_seq) {
+          if (owned_seq % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          const int mt = (p.rank * p.seg_m_tiles + um) * p.sub_tiles + subt;
+          if (mt * BM >= p.M) continue;
+          const int lin = mt * p.n_tiles + nt;
+          const uint64_t ta0 = cprof ? globaltimer_ns() : 0;
+          if (ctid == 0) s_flags[1] = 1;
+          named_bar_sync(1, kCommThreads);
+          if (ctid < p.R &&
+              !wait_flag_ge(p.peer_tile_flags[p.rank] + ctid * p.ticket_stride + lin, p.round, env, SITE_RS_TILE,
+                            (ctid << 24) | lin))
+            s_flags[1] = 0;
+          named_bar_sync(1, kCommThreads);     // also orders the reads below after the acquires
+          ok = s_flags[1] != 0;
+          named_bar_sync(1, kCommThreads);
+          if (!ok) break;
+          const uint64_t ta1 = cprof ? globaltimer_ns() : 0;
+          const int rows = min(BM, p.M - mt * BM);
+          const int cols = min(BN, p.N - nt * BN);
+          const int vpr = cols >> 3;
+          const int total = rows * vpr;
+          const int lrow0 = mt * BM - p.rank * p.m_per_rank;
+          constexpr int kU = 16;
+          for (int i0 = ctid; i0 < total; i0 += kU * kCommThreads) {
+            uint4 val[kU];
+            // all loads of the batch are issued before the first store needs its value; pieces
+            // past the end of the block re-read its last piece (no branch between the loads)
+#pragma unroll
+            for (int u2 = 0; u2 < kU; ++u2) {
+              const int idx = min(i0 + u2 * kCommThreads, total - 1);
+              const int r = idx / vpr;
+              const int v = idx - r * vpr;
+              const int64_t off = static_cast<int64_t>(mt * BM + r) * p.N + nt * BN + v * 8;
+              val[u2] = multimem_ld_reduce_add_v4<kBf16>(mc_in + off * 2);
+            }
+#pragma unroll
+            for (int u2 = 0; u2 < kU; ++u2) {
+              const int idx = i0 + u2 * kCommThreads;
+              if (idx >= total) break;
+              const int r = idx / vpr;
+              const int v = idx - r * vpr;
+              st_global_v4(reinterpret_cast<uint8_t*>(p.c) +
+                               (static_cast<int64_t>(lrow0 + r) * p.ldc + nt * BN + v * 8) * 2,
+                           val[u2]);
+            }
+          }
+          if (cprof) {
+            acc_aw += ta1 - ta0;
+            acc_ak += globaltimer_ns() - ta1;
+          }
+        }
+      }
+      if (cprof) {
+        prof[PROF_AR_A_WAIT] = acc_aw;
+        prof[PROF_AR_A_WORK] = acc_ak;
+        prof[PROF_AR_A_DONE_AT] = globaltimer_ns() - t_kernel0;
       }
     } else if (p.op == OP_AR2 && p.R > 1) {
       const int tickets = p.unit_m * p.sub_tiles * p.n_tiles;

@@ -43,7 +43,7 @@ static EncodeTiledFn encode_fn() {
 
 // Row-major [rows, cols] 16-bit matrix, box = 128 rows x 64 columns, 128-byte swizzle.
 static CUtensorMap make_tmap(const void* base, int64_t rows, int64_t cols, int64_t row_stride_elems,
-                             bool bf16) {
+                             bool bf16, int box_rows = 128) {
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
     throw std::runtime_error("tridist_b200: TMA base address must be 16-byte aligned");
   if ((row_stride_elems * 2) % 16 != 0)
@@ -51,7 +51,7 @@ static CUtensorMap make_tmap(const void* base, int64_t rows, int64_t cols, int64
   CUtensorMap m;
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_stride_elems) * 2};
-  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = encode_fn()(&m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                            2, const_cast<void*>(base), gdim, gstride, box, estr,
@@ -152,6 +152,7 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, int cta_mt, G
     throw std::runtime_error("tridist_b200: segment order needs rows per rank % 128 == 0");
   for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
   p.strided_interleave = d.strided_interleave;
+  p.seg_interleave = (d.sched == SCHED_SEGMENT) ? d.seg_interleave : 0;
   p.list_len = d.list_len;
   p.swiglu_up_row0 = d.swiglu_up_row0;
   p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;
@@ -344,7 +345,7 @@ std::vector<std::string> plan_check(const GemmPlanDesc& d, const PlanExtents& e,
       bad.push_back("rows per rank * ranks differs from M");
   }
   if (multi && (d.op == OP_RS || d.op == OP_AR1 || d.op == OP_AR2)) {
-    const int64_t plane = (d.op == OP_RS ? static_cast<int64_t>(p.m_per_rank) : d.M) * d.N;
+    const int64_t plane = ((d.op == OP_RS && !d.nvls) ? static_cast<int64_t>(p.m_per_rank) : d.M) * d.N;
     need(d.nvls ? "local partial plane" : "partial slots",
          (static_cast<int64_t>(d.R - 1) * d.slot_stride * (d.nvls ? 0 : 1) + plane) * 2, e.slot_bytes, "bytes");
     if (!d.nvls && d.slot_stride < plane)
@@ -378,6 +379,16 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
       if (d.mc_part[par] == 0 || d.mc_res[par] == 0 || d.mc_part[par] % 16 != 0 || d.mc_res[par] % 16 != 0)
         throw std::runtime_error("tridist_b200: switch-reduced all-reduce needs 16-byte aligned multicast addresses");
   }
+  if (d.nvls && d.op == OP_RS && d.R > 1) {
+    if (d.slot_stride != 0 || d.sched != SCHED_SEGMENT || !d.seg_interleave)
+      throw std::runtime_error("tridist_b200: switch-reduced reduce-scatter keeps partials local (slot_stride = 0) "
+                               "and walks the owners' segments in lockstep");
+    if (d.ldc % 8 != 0 || d.c % 16 != 0)
+      throw std::runtime_error("tridist_b200: switch-reduced reduce-scatter needs a 16-byte aligned c");
+    for (int par = 0; par < 2; ++par)
+      if (d.mc_part[par] == 0 || d.mc_part[par] % 16 != 0)
+        throw std::runtime_error("tridist_b200: switch-reduced reduce-scatter needs a 16-byte aligned multicast address");
+  }
   if (d.K % 8 != 0) throw std::runtime_error("tridist_b200: K must be a multiple of 8");
   if (d.N % 8 != 0) throw std::runtime_error("tridist_b200: N must be a multiple of 8");
   auto* plan = new GemmPlan();
@@ -397,7 +408,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     // tiles that stay on this GPU leave through staged TMA stores when c can carry a tensor map
     p.c_tma = 0;
     if (d.c != 0 && d.c % 16 == 0 && (d.ldc * 2) % 16 == 0 && (d.R == 1 || d.op == OP_PLAIN || d.op == OP_AG)) {
-      p.tma_c = make_tmap(reinterpret_cast<void*>(d.c), d.M, d.N, d.ldc, d.bf16);
+      p.tma_c32 = make_tmap(reinterpret_cast<void*>(d.c), d.M, d.N, d.ldc, d.bf16, 32);
       p.c_tma = 1;
     }
     p.tma_a = make_tmap(reinterpret_cast<void*>(d.a), d.a_rows, d.K, d.lda, d.bf16);
@@ -408,7 +419,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
     p.res_is_c = d.res_is_c;
-    p.nvls = (d.nvls && d.op == OP_AR2 && d.R > 1) ? 1 : 0;
+    p.nvls = (d.nvls && (d.op == OP_AR2 || d.op == OP_RS) && d.R > 1) ? 1 : 0;
     p.mc_part = reinterpret_cast<void*>(d.mc_part[par]);
     p.mc_res = reinterpret_cast<void*>(d.mc_res[par]);
     for (int r = 0; r < d.R; ++r) {
@@ -426,7 +437,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     }
     if (d.R > 1 && (d.op == OP_RS || d.op == OP_AR1 || d.op == OP_AR2)) {
       // store maps over this rank's slot inside every rank's slot buffer
-      const int64_t slot_rows = (d.op == OP_RS) ? p.m_per_rank : d.M;
+      const int64_t slot_rows = (d.op == OP_RS && !p.nvls) ? p.m_per_rank : d.M;
       for (int r = 0; r < d.R; ++r) {
         uint8_t* base = reinterpret_cast<uint8_t*>(p.peer_slots[r]) +
                         static_cast<int64_t>(d.rank) * d.slot_stride * 2;

@@ -31,6 +31,7 @@ struct GemmPlanDesc {
   int seg_order[8] = {0, 1, 2, 3, 4, 5, 6, 7};
   int64_t order_table = 0;
   int strided_interleave = 0;
+  int seg_interleave = 0;   // SCHED_SEGMENT: all ranks walk the segments in lockstep (tile k of every segment, then k + 1)
   int64_t tile_list = 0;
   int list_len = 0;
   int swiglu_up_row0 = 0;

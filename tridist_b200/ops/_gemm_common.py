@@ -84,7 +84,7 @@ PROF_SLOTS = ["load_flag_wait", "load_empty_wait", "mma_full_wait", "mma_tmem_wa
               "ar_collect_wait", "ar_collect_copy", "epi_done_at", "ar_owner_done_at",
               # time stamps (since the CTA started) of the last tile each role handled
               "tl_acc_ready", "tl_staged", "tl_stored", "tl_flagged", "tl_own_seen", "tl_own_loaded",
-              "tl_own_fenced", "tl_own_flagged", "tl_col_seen", "tl_comm_start", "tl_own_it0"]
+              "tl_own_fenced", "tl_own_flagged", "tl_col_seen", "tl_comm_start", "tl_own_it0", "sk_wait"]
 PROF_WIDTH = 32
 _prof_buf: Optional[torch.Tensor] = None
 

@@ -51,6 +51,12 @@ def native():
     return _build.load()
 
 
+def _symm_mem_module():
+    """torch's symmetric-memory allocator (import kept in one place so that tests can stand in for it)."""
+    import torch.distributed._symmetric_memory as symm_mem
+    return symm_mem
+
+
 # ---------------------------------------------------------------------------
 # Symmetric buffers
 # ---------------------------------------------------------------------------
@@ -203,11 +209,23 @@ class ProcessWorld(_WorldBase):
             return None
         tensor = handle = None
         mc, ptrs, why = 0, [], ""
+        group = self.group if self.group is not None else dist.group.WORLD
+        # Agree first, rendezvous second: a rank that cannot even allocate must not leave the
+        # others blocked inside the allocator's rendezvous (a different collective).
+        symm_mem = None
         try:
-            import torch.distributed._symmetric_memory as symm_mem
-            group = self.group if self.group is not None else dist.group.WORLD
+            symm_mem = _symm_mem_module()
             nbytes = (int(nbytes) + 255) // 256 * 256
             tensor = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", self.device))
+        except Exception as exc:          # missing API, unsupported driver, out of memory
+            why = f"{type(exc).__name__}: {exc}"
+        can = [None] * self.num_ranks
+        dist.all_gather_object(can, why, group=self.group)
+        if any(can):
+            self.multicast_unavailable = "; ".join(f"rank {r}: {w}" for r, w in enumerate(can) if w)
+            del tensor
+            return None
+        try:
             handle = symm_mem.rendezvous(tensor, group)
             mc = int(handle.multicast_ptr or 0)
             ptrs = [int(x) for x in handle.buffer_ptrs]
@@ -215,12 +233,12 @@ class ProcessWorld(_WorldBase):
                 why = "no multicast address"
             elif len(ptrs) != self.num_ranks or ptrs[self.rank] != tensor.data_ptr():
                 mc, why = 0, "unexpected peer pointer table"
-        except Exception as exc:          # missing API, unsupported driver, refused rendezvous
+        except Exception as exc:          # refused rendezvous (raised on every rank or on none)
             mc, why = 0, f"{type(exc).__name__}: {exc}"
         oks = [None] * self.num_ranks
-        dist.all_gather_object(oks, bool(mc), group=self.group)
-        if not all(oks):
-            self.multicast_unavailable = why or "a peer has no multicast support"
+        dist.all_gather_object(oks, why, group=self.group)
+        if any(oks):
+            self.multicast_unavailable = "; ".join(f"rank {r}: {w}" for r, w in enumerate(oks) if w)
             del handle, tensor
             return None
         buf = McBuffer(nbytes=nbytes, rank=self.rank, peer_ptrs=ptrs, device=self.device, _owner=self,

@@ -62,6 +62,38 @@ def time_op(fn: Callable[[], None], iters: int = 20, warmup: int = 3, flush: boo
             "iters": iters}
 
 
+def time_pair(fn_a: Callable[[], None], fn_b: Callable[[], None], iters: int = 20, warmup: int = 3,
+              flush: bool = True, group=None, barrier: Optional[Callable[[], None]] = None):
+    """Times two implementations of one operator in alternation (A, B, A, B, ...), each call behind
+    its own L2 flush and device barrier: both see the same clocks and power state, which a
+    power-capped GPU does not give to two loops run one after the other. Returns the two
+    ``time_op``-style dictionaries."""
+    for _ in range(warmup):
+        fn_a()
+        fn_b()
+    torch.cuda.synchronize()
+    pairs = ([], [])
+    for _ in range(iters):
+        for which, fn in enumerate((fn_a, fn_b)):
+            if flush:
+                flush_l2()
+            if barrier is not None:
+                barrier()
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            pairs[which].append((e0, e1))
+    torch.cuda.synchronize()
+    out = []
+    for which in range(2):
+        times = max_over_ranks([a.elapsed_time(b) for a, b in pairs[which]], group)
+        out.append({"mean": statistics.fmean(times), "p50": statistics.median(times), "min": min(times),
+                    "iters": iters})
+    return out[0], out[1]
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region runs (read-only)."""
 
