@@ -65,6 +65,7 @@ constexpr int kCommWarp0 = 6;
 constexpr int kCommThreads = 128;
 constexpr int kEpiThreads = 128;
 constexpr int kMaxSlices = 8;     // K ranges a remainder tile can be cut into
+constexpr int kPushSlots = 12;    // 16 KB pieces in flight per pushing CTA (all-gather)
 
 enum GemmOp : int32_t { OP_PLAIN = 0, OP_AG = 1, OP_RS = 2, OP_AR1 = 3, OP_AR2 = 4 };
 enum EpiMode : int32_t { EPI_STORE = 0, EPI_SWIGLU = 1 };
@@ -531,8 +532,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   uint64_t* tmem_full_bar = bars + 2 * TS::kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* drain_bar = tmem_empty_bar + 2;
-  uint64_t* push_bar = drain_bar + 1;            // 2 barriers of the all-gather push ring
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + 2);
+  uint64_t* push_bar = drain_bar + 1;            // barriers of the all-gather push ring
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + kPushSlots);
   int32_t* s_order = reinterpret_cast<int32_t*>(tmem_slot + 4);
   // s_flags[0]: an epilogue warp gave up; [1]: outcome of the comm warps' last wait; [2]: the
   // all-gather push of this CTA no longer uses the staging area; [3]: the epilogue's copy of [2]
@@ -561,8 +562,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       mbar_init(&tmem_empty_bar[b], 4 * kCtaM);
     }
     mbar_init(drain_bar, 1);
-    mbar_init(&push_bar[0], 1);
-    mbar_init(&push_bar[1], 1);
+    for (int i = 0; i < kPushSlots; ++i) mbar_init(&push_bar[i], 1);
     s_flags[0] = 0;
     s_flags[1] = 1;
     s_flags[2] = pushes ? 0 : 1;
@@ -614,6 +614,16 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool swiglu = p.epi == EPI_SWIGLU;
       const int up_row0 = p.swiglu_up_row0;
       const CUtensorMap* const bmap = &p.tma_b;
+      if (pushes) {
+        // the operand ring carries this CTA's part of the all-gather push first (the pushing
+        // thread's own waits are bounded, so this one ends too; the limit is a backstop)
+        const uint64_t t0 = globaltimer_ns();
+        while (s_flags[2] == 0) {
+          __nanosleep(200);
+          if (globaltimer_ns() - t0 > 2 * env.timeout_ns) { ok = false; break; }
+        }
+        fence_proxy_async_smem();
+      }
       WorkIter wit;
       WorkItem wi;
       while (ok && wit.next(wsched, my_worker, k_blocks, wi)) {
@@ -816,7 +826,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           // 0 is free, while accumulator 1 is still being drained; the stages stay occupied
           // until half 1 has consumed them too.
           const uint32_t par_free = static_cast<uint32_t>(it & 1) ^ 1u;
-          const int ahead = (probe != 0) ? 0 : min(static_cast<int>(TS::kStages), nkb);
+          const int ahead = (probe == 1 || probe == 2) ? 0 : min(static_cast<int>(TS::kStages), nkb);
           ok = wait_acc_free(0, par_free);
           if (!ok) break;
           tc_fence_after_sync();
@@ -1185,7 +1195,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           constexpr int kWarpBox = 32 * 128;
           uint8_t* const wbox = staging + q * (2 * kWarpBox);
           const int out_row0 = m_tile * BM + q * 32;
-          uint32_t ra[32], rb[32];           // accumulator columns in flight (plain store only)
+          uint32_t rab[64];                  // accumulator columns in flight (plain store only)
 #pragma unroll
           for (int j = 0; j < BN / 64; ++j) {
             if (swiglu && j >= BN / 128) break;
@@ -1208,20 +1218,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               }
             } else {
               // the loads of box j were issued while box j - 1 was being staged
-              if (j == 0) {
-                tmem_ld_32x32b_x32(taddr, ra);
-                tmem_ld_32x32b_x32(taddr + 32, rb);
-              }
+              if (j == 0) tmem_ld_32x32b_x64(taddr, rab);
               tmem_ld_wait();
 #pragma unroll
               for (int e = 0; e < 16; ++e) {
-                pk[e] = pack2<kBf16>(__uint_as_float(ra[2 * e]), __uint_as_float(ra[2 * e + 1]));
-                pk[16 + e] = pack2<kBf16>(__uint_as_float(rb[2 * e]), __uint_as_float(rb[2 * e + 1]));
+                pk[e] = pack2<kBf16>(__uint_as_float(rab[2 * e]), __uint_as_float(rab[2 * e + 1]));
+                pk[16 + e] = pack2<kBf16>(__uint_as_float(rab[32 + 2 * e]), __uint_as_float(rab[32 + 2 * e + 1]));
               }
-              if (j + 1 < BN / 64 && out_col0 + (j + 1) * 64 < n_cols) {
-                tmem_ld_32x32b_x32(taddr + (j + 1) * 64, ra);
-                tmem_ld_32x32b_x32(taddr + (j + 1) * 64 + 32, rb);
-              }
+              if (j + 1 < BN / 64 && out_col0 + (j + 1) * 64 < n_cols)
+                tmem_ld_32x32b_x64(taddr + (j + 1) * 64, rab);
             }
             // the store that last read this box was issued two groups ago (any group for j = 0)
             if (lane == 0) {
@@ -1323,21 +1328,28 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // Push this rank's shard to every peer, nearest-next rank first, so that at any
       // moment each rank receives from exactly one sender. One work item is one `part`
       // of one chunk for one destination. A single thread drives the copy engine of
-      // the SM: 16 KB pieces are bulk-loaded into a two-slot shared-memory ring and
-      // bulk-stored to the peer, so the push costs no load/store-unit bandwidth and
-      // NVLink sees large writes.
+      // the SM: 16 KB pieces are bulk-loaded into a ring of kPushSlots slots and bulk-stored
+      // to the peer, so the push costs no load/store-unit bandwidth and NVLink sees large
+      // writes. The ring is the operand ring of the GEMM: a pushing CTA computes nothing until
+      // its part of the push is done (its producer warp waits for s_flags[2]), which gives the
+      // copy engine a dozen pieces in flight instead of two and keeps the push from competing
+      // with the CTA's own operand loads.
       if (ctid == 0) {
         constexpr uint32_t kPiece = 16384;
+        constexpr int kLag = kPushSlots / 2;     // stores that may still be reading their slot
+        static_assert(kPushSlots * kPiece <= TS::kStages * TS::kStageBytes, "push ring exceeds the operand ring");
         const int64_t chunk_bytes = static_cast<int64_t>(p.chunk_rows) * p.K * 2;
         const int64_t part_bytes = chunk_bytes / p.push_parts;   // host guarantees % 16 == 0
         const int items_per_dest = p.n_chunks * p.push_parts;
         const int items = (p.R - 1) * items_per_dest;
         const int pieces = static_cast<int>((part_bytes + kPiece - 1) / kPiece);
-        uint32_t par[2] = {0u, 0u};
+        uint32_t par_mask = 0u;                  // phase parity of every slot's barrier
         bool ok = true;
-        const int pushers = (p.push_ctas > 0 && p.push_ctas < static_cast<int>(gridDim.x))
-                                ? p.push_ctas : static_cast<int>(gridDim.x);
-        for (int item = blockIdx.x; ok && blockIdx.x < pushers && item < items; item += pushers) {
+        auto piece_bytes = [&](int i) -> uint32_t {
+          const int64_t left = part_bytes - static_cast<int64_t>(i) * kPiece;
+          return static_cast<uint32_t>(left < kPiece ? left : kPiece);
+        };
+        for (int item = blockIdx.x; ok && pushes && item < items; item += push_grid) {
           const int di = item / items_per_dest;
           const int rem = item - di * items_per_dest;
           const int ck = rem / p.push_parts;
@@ -1347,31 +1359,30 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a_local) + src_off;
           uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_ws[dest]) +
                          static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2 + src_off;
-          auto piece_bytes = [&](int i) -> uint32_t {
-            const int64_t left = part_bytes - static_cast<int64_t>(i) * kPiece;
-            return static_cast<uint32_t>(left < kPiece ? left : kPiece);
+          auto load_piece = [&](int i) {
+            const int sl = i % kPushSlots;
+            mbar_arrive_expect_tx(&push_bar[sl], piece_bytes(i));
+            bulk_load_1d(ring + sl * kPiece, src + static_cast<int64_t>(i) * kPiece, piece_bytes(i), &push_bar[sl]);
           };
-          // prologue: piece 0 into slot 0 (all earlier stores were drained at the end of
-          // the previous item)
-          mbar_arrive_expect_tx(&push_bar[0], piece_bytes(0));
-          bulk_load_1d(staging, src, piece_bytes(0), &push_bar[0]);
+          // all stores of the previous item were drained: every slot is free
+          for (int i = 0; i < kPushSlots && i < pieces; ++i) load_piece(i);
           for (int i = 0; ok && i < pieces; ++i) {
-            const int b = i & 1;
-            if (i + 1 < pieces) {
-              // slot b^1 was read by the store of piece i-1: let that read finish first
-              tma_store_wait_read<0>();
-              mbar_arrive_expect_tx(&push_bar[b ^ 1], piece_bytes(i + 1));
-              bulk_load_1d(staging + (b ^ 1) * kPiece, src + static_cast<int64_t>(i + 1) * kPiece,
-                           piece_bytes(i + 1), &push_bar[b ^ 1]);
-            }
-            ok = wait_mbar(&push_bar[b], par[b], env, SITE_PIPE_FULL, 100 + b);
-            par[b] ^= 1u;
+            const int sl = i % kPushSlots;
+            ok = wait_mbar(&push_bar[sl], (par_mask >> sl) & 1u, env, SITE_PIPE_FULL, 100 + sl);
+            par_mask ^= 1u << sl;
             if (!ok) break;
-            bulk_store_1d(dst + static_cast<int64_t>(i) * kPiece, staging + b * kPiece, piece_bytes(i));
+            bulk_store_1d(dst + static_cast<int64_t>(i) * kPiece, ring + sl * kPiece, piece_bytes(i));
             tma_store_commit();
+            // the store of piece i - kLag has read its slot once at most kLag newer stores are
+            // still reading theirs: refill that slot with the piece one ring turn later
+            const int j = i - kLag;
+            if (j >= 0 && j + kPushSlots < pieces) {
+              tma_store_wait_read<kLag>();
+              load_piece(j + kPushSlots);
+            }
           }
           tma_store_wait_all<0>();             // every byte of the item has been written
-          if (!ok) break;
+          if (!ok) break;                      // (a wait ran out: its status is recorded, the ring stays unused)
           fence_acq_rel_sys();
           uint32_t* cnt = p.ag_counters + dest * p.n_chunks + ck;
           const uint32_t old = atomicAdd(cnt, 1u);
@@ -1381,7 +1392,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
             st_release_sys(p.peer_ag_flags[dest] + p.rank * p.ag_flag_stride + ck, p.round);
           }
         }
-        // every copy of this thread has completed: the staging area now belongs to the epilogue
+        // every copy of this thread has completed (or the push gave up): the operand ring and
+        // the staging area now belong to the GEMM roles of this CTA
         __threadfence_block();
         s_flags[2] = 1;
       }

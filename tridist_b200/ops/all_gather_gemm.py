@@ -20,6 +20,7 @@ double-buffered by call parity.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -60,7 +61,9 @@ class AllGatherGEMMTensorParallelContext:
 
     @property
     def max_chunks(self) -> int:
-        return max(1, (self.max_M // self.num_ranks) // self.M_PER_CHUNK)
+        """Ticket words per source: one per 128 rows of the largest shard (the granularity of a
+        call's tickets is chosen per call, see ``_ticket_rows``)."""
+        return max(1, (self.max_M // self.num_ranks) // 128)
 
     @property
     def ws_ptr(self) -> int:
@@ -102,11 +105,61 @@ def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
     return ctx
 
 
-def _push_parts(chunk_rows: int) -> int:
-    parts = 64
-    while parts > 1 and chunk_rows % parts != 0:
-        parts //= 2
+def _ticket_rows(ctx, m_pr: int) -> int:
+    """Rows per arrival ticket: ``M_PER_CHUNK`` of the context, cut down to ``TRIDIST_AG_TICKET_ROWS``
+    (default 256, the rows of one CTA tile) so that a consumer can start on a shard as soon as its
+    first rows have landed instead of waiting for all of it."""
+    rows = min(ctx.M_PER_CHUNK, m_pr)
+    want = env_int("TRIDIST_AG_TICKET_ROWS", 256)
+    if want >= 128 and want % 128 == 0 and want < rows and rows % want == 0 and m_pr // want <= 32:
+        rows = want
+    return rows
+
+
+def _push_parts(chunk_rows: int, K: int) -> int:
+    """Pieces of work a chunk's push is cut into (whole rows each, about a megabyte)."""
+    parts = 1
+    while parts < 64 and chunk_rows % (parts * 2) == 0 and (chunk_rows // (parts * 2)) * K * 2 >= (1 << 20):
+        parts *= 2
     return parts
+
+
+def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int):
+    """(pushing CTAs, scheduling rounds they sit out). The pushing CTAs carry the whole shard to
+    the peers before they compute anything; they skip as many rounds of tiles as that takes."""
+    m_tiles = M // BM
+    wide = env_int("TRIDIST_WIDE", 1) and m_tiles >= 4 and (m_pr // BM) % 4 == 0
+    pair = env_int("TRIDIST_CTA_PAIR", 1) and (m_pr // BM) % 2 == 0
+    unit_rows = 512 if (wide and pair) else (256 if pair else 128)
+    workers = 148 // (2 if pair else 1)
+    units = ((M + unit_rows - 1) // unit_rows) * ((N_out + bn_out - 1) // bn_out)
+    rounds = units / float(workers)
+    tile_us = unit_rows * 256.0 * 2.0 * K / ((2 if pair else 1) * 8192.0 * 1500.0)
+    out_bytes = (R - 1) * m_pr * K * 2.0
+    forced_ctas, forced_skip = env_int("TRIDIST_PUSH_CTAS", -1), env_int("TRIDIST_PUSH_SKIP", -1)
+
+    def push_us(ctas: int) -> float:
+        # measured: about 34 GB/s per pushing CTA (twelve 16 KB pieces in flight), 560 GB/s at most
+        return out_bytes / (min(ctas * 34.0, 560.0) * 1e3)
+
+    def skip_of(ctas: int) -> int:
+        return max(0, min(int(math.ceil(push_us(ctas) / tile_us)), max(int(rounds) - 1, 0)))
+
+    if forced_ctas >= 0:
+        ctas = forced_ctas
+    else:
+        # fewest CTA-rounds given up to the push, among the counts that finish it by 60 % of the kernel
+        step = 2 if pair else 1
+        best = None
+        for n in range(4, 33, step):
+            if push_us(n) > 0.6 * rounds * tile_us and n < 32:
+                continue
+            cost = n * skip_of(n)
+            if best is None or cost < best[0]:
+                best = (cost, n)
+        ctas = best[1] if best else 16
+    skip = forced_skip if forced_skip >= 0 else skip_of(ctas if ctas > 0 else 148)
+    return ctas, skip
 
 
 def _plan(ctx, a, b, c, swiglu=False):
@@ -141,16 +194,13 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["ag_flag_stride"] = ctx.max_chunks     # one word per (source, chunk) for every M
             d["ag_counters"] = ctx.counters.data_ptr()
             d["arrival_ns"] = ctx.arrival_ns.data_ptr() if ctx.observe else 0
-            chunk = min(ctx.M_PER_CHUNK, m_pr)
+            chunk = _ticket_rows(ctx, m_pr)
             d["chunk_rows"] = chunk
             d["n_chunks"] = m_pr // chunk
-            d["push_parts"] = _push_parts(chunk)
-            # A subset of the CTAs drives the push and joins the GEMM one round late: the copy
-            # engine of a pushing SM is busy, which slows that SM's operand loads.
-            units = ((M + 255) // 256) * ((N + (bn // 2 if swiglu else bn) - 1) // (bn // 2 if swiglu else bn))
-            rounds = units / 74.0
-            d["push_ctas"] = env_int("TRIDIST_PUSH_CTAS", 32)
-            d["push_skip_rounds"] = env_int("TRIDIST_PUSH_SKIP", 1 if rounds >= 4 else 0)
+            d["push_parts"] = _push_parts(chunk, K)
+            # A subset of the CTAs carries the push (their operand ring is the copy ring
+            # meanwhile) and joins the GEMM as many rounds late as the push takes.
+            d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn)
             debug_check(d, c_bytes=tensor_extent_bytes(c), ws_bytes=ctx.max_M * K * 2,
                         ag_flag_words=ctx.flags.nbytes // 4)
         else:
@@ -168,8 +218,7 @@ def _check_args(a, b, c, ctx):
     assert a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) == K, "a must be a contiguous [M_pr, K] shard"
     assert M % _CONSUMER_BLOCK_M == 0 and b.shape[0] % _CONSUMER_BLOCK_N == 0
     assert K % 16 == 0
-    chunk = min(ctx.M_PER_CHUNK, m_pr)
-    assert m_pr % chunk == 0
+    assert m_pr % min(ctx.M_PER_CHUNK, m_pr) == 0
     assert c.shape[0] == M and c.stride(1) == 1
 
 

@@ -10,7 +10,7 @@ Public API follows the reference (triton_dist/kernels/dcu/gemm_reduce_scatter.py
 
 Two forms of the one persistent kernel, chosen per context:
 
-switch    (three or more ranks on a fabric with multicast, the default there) partial tiles stay
+switch    (on a fabric with multicast, the default there) partial tiles stay
           in the producing rank's own plane of a multicast-bound buffer; all ranks walk the
           owners' row segments in lockstep, and the communication warps of the rank that keeps a
           tile's rows read the SUM of the R partials with ``multimem.ld_reduce`` (added inside
@@ -64,7 +64,7 @@ def create_gemm_rs_intra_node_context(max_M, N, output_dtype, rank, num_ranks, m
                                       fuse_scatter=True, transpose_weight=False, world=None,
                                       nvls: Optional[bool] = None):
     """Collective. ``fuse_scatter`` / ``transpose_weight`` accept only the reference's defaults.
-    ``nvls`` (True / False / None = by the environment: on at three or more ranks) also allocates
+    ``nvls`` (True / False / None = by the environment: on wherever the fabric has multicast) also allocates
     the multicast-bound partial planes of the switch-reduced form and checks them once with known
     integers."""
     if not fuse_scatter or transpose_weight:
@@ -81,7 +81,7 @@ def create_gemm_rs_intra_node_context(max_M, N, output_dtype, rank, num_ranks, m
         ctx.slots = world.alloc(2 * max_M * N * 2, rank)
         ctx.tile_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)
         if nvls is None:
-            nvls = ctx.mode == "nvls" or (ctx.mode == "auto" and num_ranks >= 3)
+            nvls = ctx.mode in ("nvls", "auto")
         if nvls and (max_M // num_ranks) % BM == 0:
             ctx.mc = world.alloc_multicast(2 * max_M * N * 2)
         if ctx.mc is not None and env_int("TRIDIST_NVLS_SELFTEST", 1):
