@@ -405,3 +405,160 @@ def test_tp_mlp_single_rank(mode):
         torch.cuda.synchronize()
         w.check()
         assert (y.float() - ref).abs().max().item() < 3e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# The persistent loop, the tile shapes and the edges (every CTA gets many tiles: accumulator
+# reuse, ring wrap across tiles, late-joining pushers; odd block counts; ragged M and N)
+# ---------------------------------------------------------------------------------------------
+def _rand(shape, seed, dtype, scale=0.05):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def _check_rows(out, a, b, rows=96, tol=TOL):
+    idx = torch.randperm(a.shape[0], device="cuda")[:rows]
+    ref = a[idx].float() @ b.float().t()
+    err = (out[idx].float() - ref).abs().max().item()
+    assert err < tol, err
+
+
+@pytest.mark.parametrize("variant", ["wide", "pair", "single"])
+@pytest.mark.parametrize("K", [2048, 12288])
+def test_plain_gemm_many_tiles_per_cta(variant, K, monkeypatch):
+    """16 CTAs for 4096 x 4096: every CTA (pair) walks 16 to 64 tiles, so both accumulators are
+    reused many times and the operand ring wraps across tile boundaries."""
+    from tridist_b200.ops._gemm_common import gemm_nt
+    monkeypatch.setenv("TRIDIST_WIDE", "1" if variant == "wide" else "0")
+    monkeypatch.setenv("TRIDIST_CTA_PAIR", "0" if variant == "single" else "1")
+    a, b = _rand((4096, K), 21, torch.bfloat16), _rand((4096, K), 22, torch.bfloat16)
+    out = gemm_nt(a, b, max_ctas=16)
+    torch.cuda.synchronize()
+    _check_rows(out, a, b)
+
+
+@pytest.mark.parametrize("splitk", [1, 0])
+@pytest.mark.parametrize("M,N,K,max_ctas", [(128, 2048, 4096, 0), (128, 1024, 8200, 0), (1536, 1024, 2048, 10),
+                                            (2048, 2304, 1024, 20), (640, 648, 1024, 0), (1000, 520, 776, 0),
+                                            (384, 768, 512, 0), (4224, 512, 256, 12)])
+def test_plain_gemm_edges_and_split_k(M, N, K, max_ctas, splitk, monkeypatch):
+    """Ragged M / N / K, odd numbers of row blocks under CTA pairs and 512-row tiles, and the K
+    split of the last scheduling round (2 to 8 slices; K blocks that do not divide evenly)."""
+    from tridist_b200.ops._gemm_common import gemm_nt
+    monkeypatch.setenv("TRIDIST_SPLITK", str(splitk))
+    for dt in (torch.float16, torch.bfloat16):
+        a, b = _rand((M, K), 31, dt), _rand((N, K), 32, dt)
+        out = gemm_nt(a, b, max_ctas=max_ctas)
+        torch.cuda.synchronize()
+        ref = a.float() @ b.float().t()
+        assert (out.float() - ref).abs().max().item() < TOL
+
+
+def test_split_k_slices_are_used(monkeypatch):
+    from tridist_b200.ops._gemm_common import BM, OP_PLAIN, SCHED_NATURAL
+    C = _loaded_native()
+    for M, N, K in [(128, 2048, 4096), (128, 8192, 3584), (8192, 6144, 12288)]:
+        cuts = C.splitk_dump(dict(op=OP_PLAIN, sched=SCHED_NATURAL, bn=256 if M > 128 else 128, R=1, rank=0,
+                                  M=M, N=N, K=K), 148)
+        assert cuts and all(2 <= c[3] <= 8 for c in cuts)
+
+
+@pytest.mark.parametrize("tiles", ["single", "pair", "wide"])
+def test_fused_ops_emulated_many_tiles_per_cta(tiles, monkeypatch):
+    """Two virtual ranks, 8 CTAs each, 2048-row problems: AG (pushing CTAs join late), RS and both
+    AR forms walk many tiles per CTA, on single CTAs, CTA pairs and 512-row pair tiles."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    from tridist_b200.ops.gemm_allreduce import create_gemm_ar_intra_node_context, gemm_ar_emulated
+    from tridist_b200.ops.gemm_reduce_scatter import create_gemm_rs_intra_node_context, gemm_rs_emulated
+    monkeypatch.setenv("TRIDIST_MAX_CTAS", "8")
+    monkeypatch.setenv("TRIDIST_EMU_PAIR", "0" if tiles == "single" else "1")
+    monkeypatch.setenv("TRIDIST_WIDE", "1" if tiles == "wide" else "0")
+    monkeypatch.setenv("TRIDIST_PUSH_CTAS", "4")
+    monkeypatch.setenv("TRIDIST_PUSH_SKIP", "1")
+    R, dt = 2, torch.bfloat16
+    w = _emu(R)
+    M, N, K = 2048, 1024, 768
+    m_pr = M // R
+    ag = [create_ag_gemm_intra_node_context(M, K, dt, dt, r, R, M_PER_CHUNK=512, world=w) for r in range(R)]
+    rs = [create_gemm_rs_intra_node_context(M, N, dt, r, R, world=w) for r in range(R)]
+    ar = [create_gemm_ar_intra_node_context(M, N, dt, dt, r, R, M_PER_CHUNK=64, world=w) for r in range(R)]
+    for it in range(2):
+        a_sh = [_rand((m_pr, K), 40 + 7 * it + r, dt) for r in range(R)]
+        bw = [_rand((N, K), 50 + 7 * it + r, dt) for r in range(R)]
+        c = [torch.empty(M, N, dtype=dt, device="cuda") for _ in range(R)]
+        ag_gemm_emulated(ag, a_sh, bw, c)
+        torch.cuda.synchronize()
+        w.check()
+        full = torch.cat(a_sh, 0)
+        for r in range(R):
+            _check_rows(c[r], full, bw[r])
+        a_k = [_rand((M, K), 60 + 7 * it + r, dt) for r in range(R)]
+        ref = sum(a_k[s].float() @ bw[s].float().t() for s in range(R))
+        outs = gemm_rs_emulated(rs, a_k, bw)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(R):
+            assert (outs[r].float() - ref[r * m_pr:(r + 1) * m_pr]).abs().max().item() < 2e-2
+        for mode in ("one_shot", "two_shot"):
+            cc = [torch.empty(M, N, dtype=dt, device="cuda") for _ in range(R)]
+            gemm_ar_emulated(ar, a_k, bw, cc, mode=mode)
+            torch.cuda.synchronize()
+            w.check()
+            for r in range(R):
+                assert (cc[r].float() - ref).abs().max().item() < 2e-2, mode
+                assert torch.equal(cc[r], cc[0])
+
+
+@pytest.mark.parametrize("R,M", [(4, 768), (2, 384), (4, 1280)])
+def test_gemm_rs_emulated_rows_per_rank_not_a_block_multiple(R, M):
+    """Rows per rank of 192 / 320: row blocks with two owners take the per-row bulk path, and two
+    owners of one block publish before either waits."""
+    from tridist_b200.ops.gemm_reduce_scatter import create_gemm_rs_intra_node_context, gemm_rs_emulated
+    w = _emu(R)
+    dt = torch.float16
+    N, kl = 640, 320
+    ctxs = [create_gemm_rs_intra_node_context(M, N, dt, r, R, world=w) for r in range(R)]
+    for it in range(2):
+        a_all = [_rand((M, kl), 70 + it * 9 + r, dt) for r in range(R)]
+        b_all = [_rand((N, kl), 80 + it * 9 + r, dt) for r in range(R)]
+        outs = gemm_rs_emulated(ctxs, a_all, b_all)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
+        m_pr = M // R
+        for r in range(R):
+            assert (outs[r].float() - ref[r * m_pr:(r + 1) * m_pr]).abs().max().item() < TOL
+
+
+def test_fused_kernel_gives_up_cleanly_when_a_shard_never_arrives(monkeypatch):
+    """The allowed form of a failure test: virtual rank 1 does not push, rank 0's producer waits
+    for its shard with a 20 ms limit, the wait runs out, every role of the kernel unwinds (loads
+    drained, MMAs retired, TMEM freed), the status names the site, and the next launch on the same
+    context works."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    from tridist_b200.parallel.runtime import TriDistError
+    monkeypatch.setenv("TRIDIST_WAIT_TIMEOUT_MS", "20")
+    R, dt = 2, torch.float16
+    w = _emu(R)
+    m_pr, K, N = 256, 512, 512
+    ctxs = [create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, r, R, M_PER_CHUNK=128, world=w) for r in range(R)]
+    a = [_rand((m_pr, K), 90 + r, dt) for r in range(R)]
+    b = [_rand((N, K), 95 + r, dt) for r in range(R)]
+    c = [torch.empty(m_pr * R, N, dtype=dt, device="cuda") for _ in range(R)]
+    ag_gemm_emulated(ctxs, a, b, c)                      # a good round first
+    torch.cuda.synchronize()
+    w.check()
+    ag_gemm_emulated(ctxs, a, b, c, mute_ranks=[1])      # rank 1's shard never arrives at rank 0
+    torch.cuda.synchronize()
+    with pytest.raises(TriDistError, match="all-gather chunk ticket"):
+        w.check()
+    st = w.status()
+    assert st[0] == 1 and st[1] == 0 and st[2] == 1      # flag wait timed out, on rank 0, at the chunk ticket
+    w.clear_status()
+    ag_gemm_emulated(ctxs, a, b, c)                      # the context is still usable
+    torch.cuda.synchronize()
+    w.check()
+    full = torch.cat(a, 0).float()
+    for r in range(R):
+        assert (c[r].float() - full @ b[r].float().t()).abs().max().item() < TOL

@@ -65,7 +65,10 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t tick
   return static_cast<int32_t>(v - ticket) >= 0;
 }
 
-// Wait for an mbarrier phase with the same limit.
+// Wait for an mbarrier phase. The limit is twice that of a flag wait: the pipeline barriers of a
+// kernel depend on its flag waits (no operands without the ticket), so when a ticket never
+// comes the flag wait is the one that runs out first and names the cause; the pipeline waits
+// then leave through the abort word.
 __device__ __forceinline__ bool wait_mbar(uint64_t* bar, uint32_t parity, const WaitEnv& env,
                                           uint32_t site, uint32_t aux) {
 #pragma unroll 1
@@ -77,7 +80,7 @@ __device__ __forceinline__ bool wait_mbar(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 31u) == 0u) {
       if (aborted(env)) return false;
-      if (globaltimer_ns() - t0 > env.timeout_ns) {
+      if (globaltimer_ns() - t0 > 2 * env.timeout_ns + 10000000ull) {
         report_failure(env, ST_TIMEOUT_MBAR, site, parity, 0u, aux);
         return false;
       }

@@ -451,11 +451,13 @@ __device__ __forceinline__ void add_rows32_from_sources(float (&acc)[32], const 
   }
 }
 
+// Stores the first `cols` (a multiple of 8, at most 32) of 32 consecutive values of a row.
 template <bool kBf16>
-__device__ __forceinline__ void store_row32(void* dst, const float (&acc)[32]) {
+__device__ __forceinline__ void store_row32(void* dst, const float (&acc)[32], int cols = 32) {
   uint4* d = reinterpret_cast<uint4*>(dst);
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
+    if (q * 8 >= cols) break;
     uint4 v;
     v.x = pack2<kBf16>(acc[q * 8 + 0], acc[q * 8 + 1]);
     v.y = pack2<kBf16>(acc[q * 8 + 2], acc[q * 8 + 3]);
@@ -1273,7 +1275,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           const bool active = row_ok && ocol < n_cols;
           if (active) {
             if (local_tile) {
-              store_row32<kBf16>(c_base + (static_cast<int64_t>(row) * ldc + ocol) * 2, acc);
+              // (N is a multiple of 8, not necessarily of 32: the last chunk of a row can be short)
+              store_row32<kBf16>(c_base + (static_cast<int64_t>(row) * ldc + ocol) * 2, acc, n_cols - ocol);
             } else if (op == OP_RS) {
               if (owner == p.rank) {
                 const int lrow = row - owner * p.m_per_rank;

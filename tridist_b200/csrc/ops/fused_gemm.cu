@@ -545,20 +545,34 @@ void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_tabl
   ++g_launches;
 }
 
-template <int BN, bool kBf16>
+template <int BN, bool kBf16, int kCtaM, int kMT>
 static void launch_emulated(const GemmParams* dev, int grid_x, int vranks, cudaStream_t stream) {
-  set_attr_once<BN, kBf16, 1, true, 1>();
+  set_attr_once<BN, kBf16, kCtaM, true, kMT>();
   GemmParams dummy;
   std::memset(&dummy, 0, sizeof(dummy));
-  void* args[2] = {&dummy, &dev};
-  // Cooperative launch: the runtime refuses the launch unless every CTA of
+  // Cooperative launch: the runtime refuses the launch unless every CTA (every CTA pair) of
   // every emulated rank can be resident at once, which the cross-rank waits need.
-  check(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<BN, kBf16, 1, true, 1>),
-                                    dim3(grid_x, vranks, 1), dim3(kThreads, 1, 1), args,
-                                    TileShape<BN, 1, true, 1>::kSmemBytes, stream),
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid_x, vranks, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = TileShape<BN, kCtaM, true, kMT>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = kCtaM;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  check(cudaLaunchKernelEx(&cfg, fused_gemm_kernel<BN, kBf16, kCtaM, true, kMT>, dummy, dev),
         "fused_gemm_kernel cooperative launch");
 }
 
+// `skip_comm`: bit 0 = every rank skips its communication (GEMM-only decomposition); bit 8 + r =
+// virtual rank r alone neither pushes nor waits (the others then wait for it in vain: the bounded
+// wait runs out, which is how the give-up path is exercised on one GPU).
 void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round, int parity,
                                 int skip_comm, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -566,16 +580,14 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
   if (vr < 1 || vr > kMaxRanks) throw std::runtime_error("tridist_b200: bad emulated rank count");
   GemmPlan* first = find_plan(ids[0]);
   std::vector<GemmParams> host(vr);
-  int grid_x = num_sms() / vr;
+  int grid_x = (num_sms() / vr) / first->cta_m * first->cta_m;
   for (int i = 0; i < vr; ++i) {
     GemmPlan* pl = find_plan(ids[i]);
-    if (pl->bn != first->bn || pl->bf16 != first->bf16)
+    if (pl->bn != first->bn || pl->bf16 != first->bf16 || pl->cta_m != first->cta_m || pl->cta_mt != first->cta_mt)
       throw std::runtime_error("tridist_b200: emulated ranks must share the kernel variant");
-    if (pl->cta_m != 1)
-      throw std::runtime_error("tridist_b200: emulated launches use single-CTA tiles (allow_pair = 0)");
     host[i] = pl->prm[parity & 1];
     host[i].round = round;
-    host[i].skip_comm = skip_comm;
+    host[i].skip_comm = (skip_comm & 1) | ((skip_comm >> (8 + i)) & 1);
     host[i].sk_epoch = g_sk_epoch + 1;
     if (pl->grid_x < grid_x) grid_x = pl->grid_x;
   }
@@ -592,13 +604,19 @@ void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round,
                         cudaMemcpyHostToDevice, stream),
         "cudaMemcpyAsync(params)");
   check(cudaStreamSynchronize(stream), "cudaStreamSynchronize(params)");
+#define TDB_EMU(BN_, CTAM_, MT_)                                                              \
+  do {                                                                                        \
+    if (first->bf16) launch_emulated<BN_, true, CTAM_, MT_>(first->dev_params, grid_x, vr, stream);  \
+    else launch_emulated<BN_, false, CTAM_, MT_>(first->dev_params, grid_x, vr, stream);      \
+  } while (0)
   if (first->bn == 256) {
-    if (first->bf16) launch_emulated<256, true>(first->dev_params, grid_x, vr, stream);
-    else launch_emulated<256, false>(first->dev_params, grid_x, vr, stream);
+    if (first->cta_m == 2 && first->cta_mt == 2) TDB_EMU(256, 2, 2);
+    else if (first->cta_m == 2) TDB_EMU(256, 2, 1);
+    else TDB_EMU(256, 1, 1);
   } else {
-    if (first->bf16) launch_emulated<128, true>(first->dev_params, grid_x, vr, stream);
-    else launch_emulated<128, false>(first->dev_params, grid_x, vr, stream);
+    TDB_EMU(128, 1, 1);
   }
+#undef TDB_EMU
   ++g_sk_epoch;
   ++g_launches;
 }

@@ -134,7 +134,10 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              allow_wide=env_int("TRIDIST_WIDE", 1), allow_splitk=env_int("TRIDIST_SPLITK", 1),
              raster_g=env_int("TRIDIST_RASTER_G", 0),
              prof=(prof_buffer().data_ptr() if prof_buffer() is not None else 0),
-             allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and getattr(world, "kind", "") != "emulated") else 0)
+             # several virtual ranks in one launch keep to single-CTA tiles unless TRIDIST_EMU_PAIR=1
+             # asks for CTA pairs there too (a cooperative launch of clusters)
+             allow_pair=1 if (env_int("TRIDIST_CTA_PAIR", 1) and
+                              (getattr(world, "kind", "") != "emulated" or env_int("TRIDIST_EMU_PAIR", 0))) else 0)
     return d
 
 

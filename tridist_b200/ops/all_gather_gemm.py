@@ -258,15 +258,18 @@ def ag_gemm_intra_node(a, b, transe_b, ctx):
     return ag_gemm_intra_node_op(a, b, c, ctx)
 
 
-def ag_gemm_emulated(ctxs, a_list, b_list, c_list, skip_comm=False, fuse_swiglu=False):
-    """All ranks of an ``EmulatedWorld`` in one cooperative launch (single-GPU protocol test)."""
+def ag_gemm_emulated(ctxs, a_list, b_list, c_list, skip_comm=False, fuse_swiglu=False, mute_ranks=()):
+    """All ranks of an ``EmulatedWorld`` in one cooperative launch (single-GPU protocol test).
+    ``mute_ranks``: virtual ranks that neither push nor wait in this call; the others wait for
+    their shards in vain, the bounded wait runs out and the kernel reports it (the give-up path)."""
     for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list):
         _check_args(a, b, c, ctx)
         if not skip_comm:
             ctx.flag_round += 1
     pids = [_plan(ctx, a, b, c, fuse_swiglu) for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list)]
     rnd = ctxs[0].flag_round
-    native().gemm_plans_launch_emulated(pids, rnd, rnd & 1, 1 if skip_comm else 0)
+    flags = (1 if skip_comm else 0) | sum(1 << (8 + int(r)) for r in mute_ranks)
+    native().gemm_plans_launch_emulated(pids, rnd, rnd & 1, flags)
     return c_list
 
 
