@@ -562,3 +562,105 @@ def test_fused_kernel_gives_up_cleanly_when_a_shard_never_arrives(monkeypatch):
     full = torch.cat(a, 0).float()
     for r in range(R):
         assert (c[r].float() - full @ b[r].float().t()).abs().max().item() < TOL
+
+
+def test_a_rank_that_gives_up_raises_every_ranks_abort_word():
+    """The abort buffer is symmetric: the kernel that runs out of time stores its code into the abort
+    word of every rank, and a kernel that leaves a wait because of a raised word records why."""
+    w = _emu(3)
+    C = _loaded_native()
+    w.clear_status()
+    words = w.peer_abort_words()
+    assert len(set(words)) == 3
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    C.wait_flag_test(flag.data_ptr(), 9, w.status_dev, words[0], 20_000_000, words)
+    torch.cuda.synchronize()
+    raised = [int(w.abort_buf.tensor(torch.int32, (1,), 0, rank=r).item()) for r in range(3)]
+    assert raised == [1, 1, 1]
+    assert w.status()[0] == 1
+    # a second waiter whose word is already raised leaves at once and records "gave up because ..."
+    from tridist_b200.parallel.runtime import TriDistError
+    w.C.status_clear(w.status_host)
+    C.wait_flag_test(flag.data_ptr(), 9, w.status_dev, words[1], 2_000_000_000, [])
+    torch.cuda.synchronize()
+    assert w.status()[0] == 5
+    with pytest.raises(TriDistError, match="another rank"):
+        w.check()
+    w.clear_status()
+    assert [int(w.abort_buf.tensor(torch.int32, (1,), 0, rank=r).item()) for r in range(3)] == [0, 0, 0]
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_ag_gemm_pull_transport_emulated(R):
+    """The tile-ready entry points: stage, arrive tickets, pull through the copy engine, ready tickets."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated
+    from tridist_b200.ops.gemm_ag_tr import create_gemm_ag_tr_context
+    w = _emu(R)
+    dt = torch.float16
+    m_pr, K, n_pr = 256, 1024, 384
+    ctxs = [create_gemm_ag_tr_context(m_pr * R, K, dt, dt, r, R, chunk_rows=128, world=w) for r in range(R)]
+    assert all(c.transport == "pull" for c in ctxs)
+    for it in range(3):
+        a = [_rand((m_pr, K), 200 + it * 5 + r, dt) for r in range(R)]
+        b = [_rand((n_pr, K), 210 + it * 5 + r, dt) for r in range(R)]
+        c = [torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda") for _ in range(R)]
+        ag_gemm_emulated(ctxs, a, b, c)
+        torch.cuda.synchronize()
+        w.check()
+        full = torch.cat(a, 0).float()
+        for r in range(R):
+            assert (c[r].float() - full @ b[r].float().t()).abs().max().item() < TOL, f"round {it} rank {r}"
+            ws = ctxs[r].workspace(ctxs[r].flag_round & 1, m_pr * R)
+            for s in range(R):                      # own shard staged, the others pulled, all bit-exact
+                assert torch.equal(ws[s * m_pr:(s + 1) * m_pr], a[s])
+
+
+def test_skew_table_modes_give_the_same_result_emulated():
+    """The full table [seq, degraded, mode, k_eff, order[R], budget[R]] read by the kernel: band-major
+    (mode 0, two row bands), source-major (mode 1), degraded (default rotation) and small spin budgets
+    only change which CTA computes which tile when."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    R = 4
+    w = _emu(R)
+    dt = torch.bfloat16
+    m_pr, K, n_pr = 512, 512, 512
+    ctxs = [create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, r, R, M_PER_CHUNK=256, world=w) for r in range(R)]
+    a = [_rand((m_pr, K), 300 + r, dt) for r in range(R)]
+    b = [_rand((n_pr, K), 310 + r, dt) for r in range(R)]
+    ref = [torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda") for _ in range(R)]
+    ag_gemm_emulated(ctxs, a, b, ref)
+    torch.cuda.synchronize()
+    w.check()
+    full = torch.cat(a, 0).float()
+    assert (ref[0].float() - full @ b[0].float().t()).abs().max().item() < 2e-2
+    for seq, (deg, mode, k_eff, budget) in enumerate([(0, 0, 2, 128), (0, 1, 2, 128), (1, 1, 2, 128), (0, 0, 2, 1)]):
+        tables = []
+        for r, ctx in enumerate(ctxs):
+            order = [r] + [x for x in range(R) if x not in (r, (r + 1) % R)] + [(r + 1) % R]
+            t = torch.tensor([seq, deg, mode, k_eff] + order + [budget] * R, dtype=torch.int32, device="cuda")
+            tables.append(t)
+            ctx.emu_order_table = t[4:4 + R]
+            ctx.emu_table_header = True
+            ctx.plans.clear()
+        out = [torch.empty_like(x) for x in ref]
+        ag_gemm_emulated(ctxs, a, b, out)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(R):
+            assert torch.equal(out[r], ref[r]), (deg, mode, k_eff, budget, r)
+
+
+def test_band_major_schedule_walks_bands_first():
+    C = _loaded_native()
+    from tridist_b200.ops._gemm_common import OP_AG, SCHED_SEGMENT
+    R, M, N = 4, 4096, 1024
+    d = dict(op=OP_AG, sched=SCHED_SEGMENT, bn=256, R=R, rank=1, M=M, N=N, K=1024, m_per_rank=M // R,
+             seg_order=[1, 0, 3, 2], chunk_rows=256, n_chunks=4, seg_bands=2, allow_wide=0)
+    tiles = sorted((t[4], t[0]) for cta in C.schedule_dump(d, 148) for t in cta)
+    rows_per_seg = (M // R) // 128
+    walk = []
+    for _, mt in tiles:
+        key = (mt // rows_per_seg, (mt % rows_per_seg) // (rows_per_seg // 2))     # (segment, band)
+        if not walk or walk[-1] != key:
+            walk.append(key)
+    assert walk == [(s, b) for b in range(2) for s in [1, 0, 3, 2]]

@@ -73,3 +73,29 @@ def test_reference_import_paths():
         assert callable(getattr(pydushmem, name))
         from tridist_b200.parallel.symm_host import SymmHost
         assert hasattr(SymmHost, name), name          # the delegate names a real method
+
+
+def test_ticket_ceiling_and_ignored_argument_warnings():
+    import warnings
+
+    import pytest
+    import torch
+
+    from tridist_b200.ops import create_gemm_ar_rd_context, create_gemm_rs_v5_context
+    from tridist_b200.ops._gemm_common import MAX_TICKETS, next_round
+    from tridist_b200.parallel.runtime import CpuWorld
+    assert next_round(41) == 42
+    with pytest.raises(RuntimeError, match="create a new one"):
+        next_round(MAX_TICKETS - 1, "reduce-scatter context")
+    w = CpuWorld(0, 1)
+    with pytest.warns(UserWarning, match="stage_slots=8 has no effect"):
+        create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, stage_slots=8, world=w)
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")                 # defaults and honoured arguments stay silent
+        ctx = create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, chunk_rows=64, world=w)
+        assert ctx.chunk_rows == 64
+        rs = create_gemm_rs_v5_context(256, 128, torch.float32, 0, 1, steady_sms=16, tail_chunk_window=2,
+                                       chunk_rows=128, world=w)
+        assert rs.reduce_ctas == 16 and rs.reduce_tail == 2
+    with pytest.warns(UserWarning, match="comm_lanes=4"):
+        create_gemm_rs_v5_context(256, 128, torch.float32, 0, 1, comm_lanes=4, world=w)

@@ -82,3 +82,7 @@ def test_no_alloc_dispatch_rejects_oversize():
     assert fn(p, p, p, p, p, p, 4, 60, 2, 8, 8, None) == -4       # hidden not a multiple of 8
     assert fn(p, p, p, p, p, p, 4, 64, 2, 8, 7, None) == -5       # recv too small for T * topk rows
     assert fn(p, p, p, p, p, p, 4, 64, 33, 8, 200, None) == -3    # topk too large
+    # a view that starts 4 bytes into its buffer: refused here, not a misaligned-address fault on the GPU
+    rc = fn(p + 4, p, p, p, p, p, 4, 64, 2, 8, 8, None)
+    assert rc == -7 and b"16-byte" in lib.tdb_noalloc_strerror(rc)
+    assert fn(p, p, p + 8, p, p, p, 4, 64, 2, 8, 8, None) == -7

@@ -61,8 +61,12 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
     for (size_t i = 0; i < v.size() && i < 8; ++i) g.seg_order[i] = v[i];
   }
   g.order_table = get<int64_t>(d, "order_table", 0);
+  g.order_table_header = get<int>(d, "order_table_header", 0);
+  g.check_residency = get<int>(d, "check_residency", 0);
   g.strided_interleave = get<int>(d, "strided_interleave", 0);
   g.seg_interleave = get<int>(d, "seg_interleave", 0);
+  g.seg_bands = get<int>(d, "seg_bands", 0);
+  fill_ptrs(d, "peer_abort", g.peer_abort, 8);
   g.tile_list = get<int64_t>(d, "tile_list", 0);
   g.list_len = get<int>(d, "list_len", 0);
   g.swiglu_up_row0 = get<int>(d, "swiglu_up_row0", 0);
@@ -73,6 +77,8 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   g.raster_g = get<int>(d, "raster_g", 0);
   fill_ptrs2(d, "peer_ws", g.peer_ws);
   fill_ptrs(d, "peer_ag_flags", g.peer_ag_flags, 8);
+  fill_ptrs(d, "peer_ag_arrive", g.peer_ag_arrive, 8);
+  g.ag_pull = get<int>(d, "ag_pull", 0);
   g.ag_counters = get<int64_t>(d, "ag_counters", 0);
   g.arrival_ns = get<int64_t>(d, "arrival_ns", 0);
   g.chunk_rows = get<int>(d, "chunk_rows", 0);
@@ -90,6 +96,8 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   fill_ptrs(d, "peer_res_flags", g.peer_res_flags, 8);
   g.res_is_c = get<int>(d, "res_is_c", 0);
   g.nvls = get<int>(d, "nvls", 0);
+  g.reduce_ctas = get<int>(d, "reduce_ctas", 0);
+  g.reduce_tail = get<int>(d, "reduce_tail", 0);
   if (d.contains("mc_part")) {
     auto v = d["mc_part"].cast<std::vector<int64_t>>();
     for (size_t i = 0; i < v.size() && i < 2; ++i) g.mc_part[i] = v[i];
@@ -165,6 +173,16 @@ static MoeDesc moe_desc_from(const py::dict& d) {
   m.done_counter = reinterpret_cast<uint32_t*>(get<int64_t>(d, "done_counter", 0));
   m.env.status = reinterpret_cast<StatusBlock*>(get<int64_t>(d, "status_dev", 0));
   m.env.abort_word = reinterpret_cast<uint32_t*>(get<int64_t>(d, "abort_word", 0));
+  {
+    int64_t pa[8] = {};
+    fill_ptrs(d, "peer_abort", pa, 8);
+    int n = 0;
+    for (int i = 0; i < 8; ++i) {
+      m.env.peer_abort[i] = reinterpret_cast<uint32_t*>(pa[i]);
+      if (pa[i] != 0) n = i + 1;
+    }
+    m.env.n_peers = static_cast<uint32_t>(n);
+  }
   m.env.timeout_ns = get<uint64_t>(d, "timeout_ns", 2000000000ull);
   m.env.rank = static_cast<uint32_t>(m.rank);
   return m;
@@ -223,13 +241,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   cur_stream());
   });
   m.def("barrier_all", [](std::vector<int64_t> peer_slots, int rank, int R, uint32_t ticket, int64_t status_dev,
-                          int64_t abort_word, uint64_t timeout_ns) {
-    barrier_launch(peer_slots, rank, R, ticket, status_dev, abort_word, timeout_ns, cur_stream());
-  });
+                          int64_t abort_word, uint64_t timeout_ns, std::vector<int64_t> peer_abort) {
+    barrier_launch(peer_slots, rank, R, ticket, status_dev, abort_word, timeout_ns, cur_stream(), peer_abort);
+  }, py::arg("peer_slots"), py::arg("rank"), py::arg("R"), py::arg("ticket"), py::arg("status_dev"),
+     py::arg("abort_word"), py::arg("timeout_ns"), py::arg("peer_abort") = std::vector<int64_t>{});
   m.def("wait_flag_test", [](int64_t flag, uint32_t ticket, int64_t status_dev, int64_t abort_word,
-                             uint64_t timeout_ns) {
-    wait_flag_test_launch(flag, ticket, status_dev, abort_word, timeout_ns, cur_stream());
-  });
+                             uint64_t timeout_ns, std::vector<int64_t> peer_abort) {
+    wait_flag_test_launch(flag, ticket, status_dev, abort_word, timeout_ns, cur_stream(), peer_abort);
+  }, py::arg("flag"), py::arg("ticket"), py::arg("status_dev"), py::arg("abort_word"), py::arg("timeout_ns"),
+     py::arg("peer_abort") = std::vector<int64_t>{});
   m.def("fill_u32", [](int64_t p, int64_t n, uint32_t v) {
     fill_u32_launch(reinterpret_cast<uint32_t*>(p), n, v, cur_stream());
   });

@@ -10,6 +10,7 @@ enum StatusCode : uint32_t {
   ST_TIMEOUT_MBAR = 2,     // an intra-CTA pipeline barrier did not flip in time
   ST_BAD_INDEX = 3,        // a computed row / tile / offset was out of range
   ST_OVERFLOW = 4,         // a receive buffer would be oversubscribed
+  ST_PEER_ABORT = 5,       // a wait was abandoned because another role or another rank gave up first
 };
 
 // Wait sites (the `site` word of the record).
@@ -22,7 +23,8 @@ enum WaitSite : uint32_t {
   SITE_MOE_META = 6,
   SITE_MOE_DISPATCH_DONE = 7,
   SITE_MOE_COMBINE_READY = 8,
-  SITE_SPLITK = 9,         // split-K finisher waiting for another slice's partial
+  SITE_SPLITK = 9,
+  SITE_AG_ARRIVE = 10,     // pull all-gather: waiting for a source to stage its chunk         // split-K finisher waiting for another slice's partial
   SITE_PIPE_FULL = 16,
   SITE_PIPE_EMPTY = 17,
   SITE_TMEM_FULL = 18,
@@ -48,6 +50,11 @@ struct WaitEnv {
   uint64_t timeout_ns;      // limit for a single wait
   uint32_t rank;
   uint32_t poll_ns;         // pause between two polls of a flag (0 = poll back to back)
+  // The same word on every rank (the abort buffer is symmetric): a rank that gives up raises all
+  // of them, so that its peers leave their waits at once instead of each burning its own limit.
+  uint32_t* peer_abort[8];
+  uint32_t n_peers;         // entries of peer_abort in use (0 = this rank's word only)
+  uint32_t pad_;
 };
 
 }  // namespace tdb

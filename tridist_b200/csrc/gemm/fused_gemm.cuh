@@ -162,6 +162,11 @@ struct alignas(64) GemmParams {
   int32_t strided_interleave;  // SCHED_STRIDED: same unit order on every rank (see tile_at)
   int32_t seg_interleave;      // SCHED_SEGMENT: position i is tile i / R of segment order[i % R]
   const int32_t* order_table;  // optional device table overriding seg_order (R entries)
+  // order_table is the order[] part of a full skew table [seq, degraded, mode, k_eff, order[R],
+  // budget[R]] (reference layout, ag_tr_pred.py:14-30): the four header words stand in front of
+  // it and R spin budgets behind it, and the kernel honours all of them (see the kernel prologue)
+  int32_t table_has_header;
+  int32_t seg_bands;           // SCHED_SEGMENT: row bands per segment walked band-major (1 = source-major)
   const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
   int32_t list_len;
   int32_t m_per_rank;      // rows per rank (AG source shard / RS owner block)
@@ -185,11 +190,14 @@ struct alignas(64) GemmParams {
   const void* a_local;             // this rank's shard (push source)
   void* peer_ws[kMaxRanks];        // workspace base (this round's parity) on every rank
   uint32_t* peer_ag_flags[kMaxRanks];  // [R][ag_flag_stride] tickets on every rank, indexed by source
-  uint32_t* ag_counters;           // local [R][n_chunks] part counters
+  uint32_t* ag_counters;           // local [R + 1][n_chunks] part counters (row R: staging of the own shard, pull)
+  uint32_t* peer_ag_arrive[kMaxRanks];  // pull: [R][ag_flag_stride] "source staged its chunk" tickets on every rank
+  int32_t ag_pull;                 // 1 = pull transport (stage, arrive, pull, ready), 0 = push
   uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
   int32_t chunk_rows, n_chunks, push_parts;
   int32_t skip_comm;
   int32_t comm_only;
+  int32_t publish_only;    // all-reduce decomposition: partial tiles are published and ticketed, nothing is reduced
   int32_t push_ctas;       // CTAs that take part in the all-gather push (0 = all)
   int32_t push_skip_rounds;  // scheduling rounds the pushing CTAs sit out
 
@@ -206,6 +214,8 @@ struct alignas(64) GemmParams {
   // OP_RS through the switch: the same, except that the owner of a tile is the rank that keeps
   // its rows and the sum is stored into that rank's c only.
   int32_t nvls;
+  int32_t reduce_ctas;             // OP_RS through the switch: CTAs that reduce in the steady phase (0 = all)
+  int32_t reduce_tail;             // ... and the number of last blocks that every CTA helps with
   void* mc_part;                   // multicast address of the partial buffer [M][N] (this parity)
   void* mc_res;                    // multicast address of the result buffer [M][N] (this parity)
 
@@ -253,12 +263,23 @@ __host__ __device__ __forceinline__ void raster_grouped(int u, int m_units, int 
 // consecutive 128-row blocks (CTA `sub` of a pair owns blocks unit_m * sub_tiles + sub * cta_mt
 // ...). `owner_key` is the unit id that decides the owning rank in the strided (two-shot
 // all-reduce) order.
+// `bands` > 1 (SCHED_SEGMENT): the segments are cut into that many row bands and the walk is
+// band-major (band 0 of every segment in `order`, then band 1 ...) instead of source-major.
 __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const int32_t* order, int pos,
-                                             int sub) {
+                                             int sub, int bands = 1) {
   TileCoord t;
   t.valid = true;
   int um = 0, nt = 0, ulin = -1;
-  if (p.sched == SCHED_SEGMENT) {
+  if (p.sched == SCHED_SEGMENT && bands > 1 && !p.seg_interleave && p.seg_m_tiles % bands == 0) {
+    const int band_units = p.seg_m_tiles / bands;
+    const int per_band = band_units * p.n_tiles;
+    const int b = pos / (p.R * per_band);
+    const int rem = pos - b * (p.R * per_band);
+    const int si = rem / per_band;
+    const int u = rem - si * per_band;
+    raster_grouped(u, band_units, p.n_tiles, p.raster_g, um, nt);
+    um += order[si] * p.seg_m_tiles + b * band_units;
+  } else if (p.sched == SCHED_SEGMENT) {
     const int per_seg = p.seg_m_tiles * p.n_tiles;
     // interleaved: every rank walks the segments in lockstep (tile k of every owner, then tile
     // k + 1 ...), so that all partials of a tile exist at about the same time on all ranks
@@ -537,9 +558,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   uint64_t* push_bar = drain_bar + 1;            // barriers of the all-gather push ring
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + kPushSlots);
   int32_t* s_order = reinterpret_cast<int32_t*>(tmem_slot + 4);
+  int32_t* s_budget = s_order + kMaxRanks;   // spin budget per source (skew table)
+  int32_t* s_tab = s_budget + kMaxRanks;     // [0]: row bands of the segment walk
   // s_flags[0]: an epilogue warp gave up; [1]: outcome of the comm warps' last wait; [2]: the
   // all-gather push of this CTA no longer uses the staging area; [3]: the epilogue's copy of [2]
-  volatile int32_t* s_flags = s_order + kMaxRanks;
+  volatile int32_t* s_flags = s_tab + 4;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -572,8 +595,25 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     mbar_fence_init();
   }
   if (threadIdx.x < kMaxRanks) {
+    // The skew table of this call: [seq, degraded, mode, k_eff | order[R] | budget[R]].
+    //   degraded = 1  the predictor stepped back: default rotation, band-major
+    //   mode = 0      band-major walk (k_eff row bands per source) in the table's order
+    //   mode = 1      source-major walk in the table's order (predicted-early sources first)
+    //   budget[s]     polls of source s's ticket between two looks at the abort word and the clock
     const int i = threadIdx.x;
-    s_order[i] = (p.order_table != nullptr && i < p.R) ? p.order_table[i] : p.seg_order[i];
+    const bool full = p.order_table != nullptr && p.table_has_header;
+    const bool degraded = full && p.order_table[-3] != 0;
+    s_order[i] = (p.order_table != nullptr && i < p.R && !degraded) ? p.order_table[i] : p.seg_order[i];
+    s_budget[i] = (full && i < p.R) ? max(1, p.order_table[p.R + i]) : 64;
+    if (i == 0) {
+      int bands = p.seg_bands > 0 ? p.seg_bands : 1;
+      if (full) {
+        const int mode = p.order_table[-2], k_eff = p.order_table[-1];
+        bands = (mode == 1 && !degraded) ? 1 : max(1, min(k_eff, p.n_chunks));
+      }
+      if (p.sched != SCHED_SEGMENT || p.seg_m_tiles % bands != 0) bands = 1;
+      s_tab[0] = bands;
+    }
   }
   if (warp == 1) {
     if constexpr (kCtaM == 2) {
@@ -589,6 +629,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const int bands = *reinterpret_cast<volatile int32_t*>(s_tab);
 
   const WaitEnv env = p.env;
   uint64_t* const prof = p.prof ? p.prof + static_cast<int64_t>(blockIdx.x) * kProfSlots : nullptr;
@@ -629,7 +670,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       WorkIter wit;
       WorkItem wi;
       while (ok && wit.next(wsched, my_worker, k_blocks, wi)) {
-        const TileCoord t = tile_at(p, s_order, wi.pos, sub);
+        const TileCoord t = tile_at(p, s_order, wi.pos, sub, bands);
         if (!t.valid) continue;
         const int m0 = t.m_tile * BM;          // first of the CTA tile's kMT * 128 rows
         const int n0 = t.n_tile * BN;
@@ -649,7 +690,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
                 if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
                 const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.ag_flag_stride + ck;
                 const uint64_t tw = prof ? globaltimer_ns() : 0;
-                ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck);
+                ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck,
+                                  static_cast<uint32_t>(s_budget[src]));
                 if (prof) acc_a += globaltimer_ns() - tw;
                 if (ok) {
                   if (ck < 32) ready_mask[src] |= 1u << ck;
@@ -788,7 +830,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       WorkIter wit;
       WorkItem wi;
       while (ok && wit.next(wsched, my_worker, k_blocks, wi)) {
-        const TileCoord t = tile_at(p, s_order, wi.pos, sub);
+        const TileCoord t = tile_at(p, s_order, wi.pos, sub, bands);
         if (!t.valid) continue;
         const int nkb = wi.kb1 - wi.kb0;
         if constexpr (kMT == 1) {
@@ -912,7 +954,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     WorkIter wit;
     WorkItem wi;
     while (alive && wit.next(wsched, my_worker, p.k_blocks, wi)) {
-      const TileCoord t = tile_at(p, s_order, wi.pos, sub);
+      const TileCoord t = tile_at(p, s_order, wi.pos, sub, bands);
       if (!t.valid) continue;
       for (int h = 0; alive && h < kMT; ++h) {
       const int buf = (kMT == 2) ? h : (it & 1);
@@ -1041,6 +1083,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           tile_publishes = true;
         }
       }
+      if (p.publish_only) tile_reduces = false;     // decomposition mode: publish and ticket, no reduce
       // the accumulator is needed after the publish phase only where this rank adds the
       // peers' partials to it (its own rows of a reduce-scatter tile)
       const bool acc_needed_later = tile_reduces && p.op == OP_RS;
@@ -1344,7 +1387,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int64_t chunk_bytes = static_cast<int64_t>(p.chunk_rows) * p.K * 2;
         const int64_t part_bytes = chunk_bytes / p.push_parts;   // host guarantees % 16 == 0
         const int items_per_dest = p.n_chunks * p.push_parts;
-        const int items = (p.R - 1) * items_per_dest;
         const int pieces = static_cast<int>((part_bytes + kPiece - 1) / kPiece);
         uint32_t par_mask = 0u;                  // phase parity of every slot's barrier
         bool ok = true;
@@ -1352,22 +1394,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           const int64_t left = part_bytes - static_cast<int64_t>(i) * kPiece;
           return static_cast<uint32_t>(left < kPiece ? left : kPiece);
         };
-        for (int item = blockIdx.x; ok && pushes && item < items; item += push_grid) {
-          const int di = item / items_per_dest;
-          const int rem = item - di * items_per_dest;
-          const int ck = rem / p.push_parts;
-          const int part = rem - ck * p.push_parts;
-          const int dest = (p.rank + 1 + di) % p.R;
-          const int64_t src_off = ck * chunk_bytes + part * part_bytes;
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.a_local) + src_off;
-          uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_ws[dest]) +
-                         static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2 + src_off;
+        // one part (part_bytes) from src to dst through the ring; returns once every byte is written
+        auto copy_part = [&](const uint8_t* src, uint8_t* dst) {
           auto load_piece = [&](int i) {
             const int sl = i % kPushSlots;
             mbar_arrive_expect_tx(&push_bar[sl], piece_bytes(i));
             bulk_load_1d(ring + sl * kPiece, src + static_cast<int64_t>(i) * kPiece, piece_bytes(i), &push_bar[sl]);
           };
-          // all stores of the previous item were drained: every slot is free
+          // all stores of the previous part were drained: every slot is free
           for (int i = 0; i < kPushSlots && i < pieces; ++i) load_piece(i);
           for (int i = 0; ok && i < pieces; ++i) {
             const int sl = i % kPushSlots;
@@ -1384,18 +1418,70 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               load_piece(j + kPushSlots);
             }
           }
-          tma_store_wait_all<0>();             // every byte of the item has been written
-          if (!ok) break;                      // (a wait ran out: its status is recorded, the ring stays unused)
+          tma_store_wait_all<0>();             // every byte of the part has been written
+        };
+        // counts a finished part of chunk (row, ck) in; true for the thread that completes the chunk
+        auto chunk_done = [&](int row, int ck) -> bool {
           fence_acq_rel_sys();
-          uint32_t* cnt = p.ag_counters + dest * p.n_chunks + ck;
+          uint32_t* cnt = p.ag_counters + row * p.n_chunks + ck;
           const uint32_t old = atomicAdd(cnt, 1u);
-          if (old + 1u == static_cast<uint32_t>(p.push_parts)) {
-            atomicExch(cnt, 0u);
-            fence_acq_rel_sys();
-            st_release_sys(p.peer_ag_flags[dest] + p.rank * p.ag_flag_stride + ck, p.round);
+          if (old + 1u != static_cast<uint32_t>(p.push_parts)) return false;
+          atomicExch(cnt, 0u);
+          fence_acq_rel_sys();
+          return true;
+        };
+        const int64_t my_slot_off = static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2;
+        if (!p.ag_pull) {
+          // ---- push: my shard into every peer's workspace, the peer's ticket when a chunk is in ----
+          const int items = (p.R - 1) * items_per_dest;
+          for (int item = blockIdx.x; ok && pushes && item < items; item += push_grid) {
+            const int di = item / items_per_dest;
+            const int rem = item - di * items_per_dest;
+            const int ck = rem / p.push_parts;
+            const int part = rem - ck * p.push_parts;
+            const int dest = (p.rank + 1 + di) % p.R;
+            const int64_t off = ck * chunk_bytes + part * part_bytes;
+            copy_part(reinterpret_cast<const uint8_t*>(p.a_local) + off,
+                      reinterpret_cast<uint8_t*>(p.peer_ws[dest]) + my_slot_off + off);
+            if (!ok) break;                    // (a wait ran out: its status is recorded)
+            if (chunk_done(dest, ck))
+              st_release_sys(p.peer_ag_flags[dest] + p.rank * p.ag_flag_stride + ck, p.round);
+          }
+        } else {
+          // ---- pull (the reference's tile-ready transport, gemm_ag_tr.py:407-449): every rank
+          // stages its shard in its own workspace and tells the peers chunk by chunk ("arrive");
+          // every rank then copies the peers' chunks out of their workspaces into its own and
+          // raises its own ready ticket, the one the consumer waits for.
+          for (int item = blockIdx.x; ok && pushes && item < items_per_dest; item += push_grid) {
+            const int ck = item / p.push_parts;
+            const int part = item - ck * p.push_parts;
+            const int64_t off = ck * chunk_bytes + part * part_bytes;
+            copy_part(reinterpret_cast<const uint8_t*>(p.a_local) + off,
+                      reinterpret_cast<uint8_t*>(p.peer_ws[p.rank]) + my_slot_off + off);
+            if (!ok) break;
+            if (chunk_done(p.R, ck))           // (row R of the counters: the staging of my own shard)
+              for (int d = 0; d < p.R; ++d)
+                if (d != p.rank) st_release_sys(p.peer_ag_arrive[d] + p.rank * p.ag_flag_stride + ck, p.round);
+          }
+          const int items = (p.R - 1) * items_per_dest;
+          for (int item = blockIdx.x; ok && pushes && item < items; item += push_grid) {
+            const int di = item / items_per_dest;
+            const int rem = item - di * items_per_dest;
+            const int ck = rem / p.push_parts;
+            const int part = rem - ck * p.push_parts;
+            const int src = (p.rank + p.R - 1 - di) % p.R;      // nearest previous rank first: the consumer's order
+            ok = wait_flag_ge(p.peer_ag_arrive[p.rank] + src * p.ag_flag_stride + ck, p.round, env, SITE_AG_ARRIVE,
+                              (src << 16) | ck);
+            if (!ok) break;
+            const int64_t off = static_cast<int64_t>(src) * p.m_per_rank * p.K * 2 + ck * chunk_bytes + part * part_bytes;
+            copy_part(reinterpret_cast<const uint8_t*>(p.peer_ws[src]) + off,
+                      reinterpret_cast<uint8_t*>(p.peer_ws[p.rank]) + off);
+            if (!ok) break;
+            if (chunk_done(src, ck))
+              st_release_sys(p.peer_ag_flags[p.rank] + src * p.ag_flag_stride + ck, p.round);
           }
         }
-        // every copy of this thread has completed (or the push gave up): the operand ring and
+        // every copy of this thread has completed (or the transfer gave up): the operand ring and
         // the staging area now belong to the GEMM roles of this CTA
         __threadfence_block();
         s_flags[2] = 1;
@@ -1411,11 +1497,19 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool cprof = prof && ctid == 0;
       uint64_t acc_aw = 0, acc_ak = 0;
       uint8_t* const mc_in = reinterpret_cast<uint8_t*>(p.mc_part);
+      // Reduce budget (the steady / tail CTA budget of the reference's windowed reduce-scatter,
+      // gemm_rs_v5.py:489-501): the first blocks are reduced by `reduce_ctas` CTAs only, the last
+      // `reduce_tail` blocks by every CTA of the grid, when nothing is left to compute.
+      const int all_ctas = static_cast<int>(gridDim.x);
+      const int steady = (p.reduce_ctas > 0 && p.reduce_ctas < all_ctas) ? p.reduce_ctas : all_ctas;
+      const int n_owned = per_seg * p.sub_tiles;
+      const int tail0 = n_owned - ((steady < all_ctas) ? max(p.reduce_tail, 0) : 0);
       for (int u = 0; ok && u < per_seg; ++u) {
         int um, nt;
         raster_grouped(u, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
         for (int subt = 0; ok && subt < p.sub_tiles; ++subt, ++owned_seq) {
-          if (owned_seq % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          const int team = owned_seq < tail0 ? steady : all_ctas;
+          if (owned_seq % team != static_cast<int>(blockIdx.x)) continue;
           const int mt = (p.rank * p.seg_m_tiles + um) * p.sub_tiles + subt;
           if (mt * BM >= p.M) continue;
           const int lin = mt * p.n_tiles + nt;
@@ -1471,7 +1565,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         prof[PROF_AR_A_WORK] = acc_ak;
         prof[PROF_AR_A_DONE_AT] = globaltimer_ns() - t_kernel0;
       }
-    } else if (p.op == OP_AR2 && p.R > 1) {
+    } else if (p.op == OP_AR2 && p.R > 1 && !p.publish_only) {
       const int tickets = p.unit_m * p.sub_tiles * p.n_tiles;
       const int units = p.unit_m * p.n_tiles;
       bool ok = true;

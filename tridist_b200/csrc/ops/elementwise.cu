@@ -116,7 +116,8 @@ __global__ void barrier_kernel(const __grid_constant__ BarrierArgs a) {
 }
 
 void barrier_launch(const std::vector<int64_t>& peer_slots, int rank, int R, uint32_t ticket,
-                    int64_t status_dev, int64_t abort_word, uint64_t timeout_ns, void* stream_) {
+                    int64_t status_dev, int64_t abort_word, uint64_t timeout_ns, void* stream_,
+                    const std::vector<int64_t>& peer_abort) {
   if (R < 1 || R > 8 || static_cast<int>(peer_slots.size()) < R)
     throw std::runtime_error("tridist_b200: barrier needs 1..8 ranks");
   BarrierArgs a{};
@@ -128,6 +129,10 @@ void barrier_launch(const std::vector<int64_t>& peer_slots, int rank, int R, uin
   a.env.abort_word = reinterpret_cast<uint32_t*>(abort_word);
   a.env.timeout_ns = timeout_ns;
   a.env.rank = static_cast<uint32_t>(rank);
+  for (size_t i = 0; i < peer_abort.size() && i < 8; ++i) {
+    a.env.peer_abort[i] = reinterpret_cast<uint32_t*>(peer_abort[i]);
+    a.env.n_peers = static_cast<uint32_t>(i + 1);
+  }
   barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(a);
   check(cudaGetLastError(), "barrier launch");
   launch_count_add(1);
@@ -141,12 +146,16 @@ __global__ void wait_flag_test_kernel(const uint32_t* flag, uint32_t ticket, Wai
 }
 
 void wait_flag_test_launch(int64_t flag, uint32_t ticket, int64_t status_dev, int64_t abort_word,
-                           uint64_t timeout_ns, void* stream_) {
+                           uint64_t timeout_ns, void* stream_, const std::vector<int64_t>& peer_abort) {
   WaitEnv env{};
   env.status = reinterpret_cast<StatusBlock*>(status_dev);
   env.abort_word = reinterpret_cast<uint32_t*>(abort_word);
   env.timeout_ns = timeout_ns;
   env.rank = 0;
+  for (size_t i = 0; i < peer_abort.size() && i < 8; ++i) {
+    env.peer_abort[i] = reinterpret_cast<uint32_t*>(peer_abort[i]);
+    env.n_peers = static_cast<uint32_t>(i + 1);
+  }
   wait_flag_test_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
       reinterpret_cast<const uint32_t*>(flag), ticket, env);
   check(cudaGetLastError(), "wait_flag_test launch");

@@ -18,12 +18,14 @@ void swiglu_launch(const void* h, void* out, int64_t rows, int64_t inter, int64_
 
 // Cross-rank barrier: writes `ticket` into slot [rank] of every rank's slot array, then
 // waits (bounded) until all R local slots reached the ticket.
+// `peer_abort`: every rank's abort word (raised together when this wait gives up); may be empty.
 void barrier_launch(const std::vector<int64_t>& peer_slots, int rank, int R, uint32_t ticket,
-                    int64_t status_dev, int64_t abort_word, uint64_t timeout_ns, void* stream);
+                    int64_t status_dev, int64_t abort_word, uint64_t timeout_ns, void* stream,
+                    const std::vector<int64_t>& peer_abort = {});
 
 // One thread waits for *flag >= ticket with the given limit; exercises timeout -> status.
 void wait_flag_test_launch(int64_t flag, uint32_t ticket, int64_t status_dev, int64_t abort_word,
-                           uint64_t timeout_ns, void* stream);
+                           uint64_t timeout_ns, void* stream, const std::vector<int64_t>& peer_abort = {});
 
 void fill_u32_launch(uint32_t* p, int64_t n, uint32_t v, void* stream);
 

@@ -73,6 +73,8 @@ struct GemmPlan {
   GemmParams* dev_params = nullptr;   // emulated multi-rank launches only
 };
 
+static int resident_ctas_of(const GemmPlan& plan);
+
 static std::mutex g_mu;
 static std::unordered_map<int64_t, GemmPlan*> g_plans;
 static int64_t g_next_plan = 1;
@@ -153,6 +155,7 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, int cta_mt, G
   for (int i = 0; i < kMaxRanks; ++i) p.seg_order[i] = (i < d.R) ? d.seg_order[i] : 0;
   p.strided_interleave = d.strided_interleave;
   p.seg_interleave = (d.sched == SCHED_SEGMENT) ? d.seg_interleave : 0;
+  p.seg_bands = (d.sched == SCHED_SEGMENT && d.seg_bands > 1) ? d.seg_bands : 1;
   p.list_len = d.list_len;
   p.swiglu_up_row0 = d.swiglu_up_row0;
   p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;
@@ -250,7 +253,7 @@ std::vector<std::vector<std::array<int, 5>>> schedule_dump(const GemmPlanDesc& d
     WorkIter wit;
     WorkItem wi;
     while (wit.next(ws, worker, p.k_blocks, wi)) {
-      const TileCoord t = tile_at(p, p.seg_order, wi.pos, sub);
+      const TileCoord t = tile_at(p, p.seg_order, wi.pos, sub, p.seg_bands);
       if (!t.valid) continue;
       // a tile cut along K appears once, with the worker that finishes it (slice 0)
       if (wi.slice > 0) continue;
@@ -401,6 +404,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     std::memset(&p, 0, sizeof(p));
     fill_schedule_fields(d, plan->cta_m, plan->cta_mt, p);
     p.order_table = reinterpret_cast<const int32_t*>(d.order_table);
+    p.table_has_header = (d.order_table != 0 && d.order_table_header) ? 1 : 0;
     p.tile_list = reinterpret_cast<const int32_t*>(d.tile_list);
     p.is_bf16 = d.bf16 ? 1 : 0;
     p.c = reinterpret_cast<void*>(d.c);
@@ -416,15 +420,22 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.tma_a_ws = p.tma_a;
     p.a_local = reinterpret_cast<const void*>(d.a);
     p.ag_counters = reinterpret_cast<uint32_t*>(d.ag_counters);
+    p.ag_pull = (d.ag_pull && d.op == OP_AG && d.R > 1) ? 1 : 0;
+    if (p.ag_pull)
+      for (int r = 0; r < d.R; ++r)
+        if (d.peer_ag_arrive[r] == 0) throw std::runtime_error("tridist_b200: pull all-gather needs the arrive ticket plane");
     p.arrival_ns = reinterpret_cast<uint64_t*>(d.arrival_ns);
     p.slot_stride = d.slot_stride;
     p.res_is_c = d.res_is_c;
     p.nvls = (d.nvls && (d.op == OP_AR2 || d.op == OP_RS) && d.R > 1) ? 1 : 0;
+    p.reduce_ctas = d.reduce_ctas;
+    p.reduce_tail = d.reduce_tail;
     p.mc_part = reinterpret_cast<void*>(d.mc_part[par]);
     p.mc_res = reinterpret_cast<void*>(d.mc_res[par]);
     for (int r = 0; r < d.R; ++r) {
       p.peer_ws[r] = reinterpret_cast<void*>(d.peer_ws[par][r]);
       p.peer_ag_flags[r] = reinterpret_cast<uint32_t*>(d.peer_ag_flags[r]);
+      p.peer_ag_arrive[r] = reinterpret_cast<uint32_t*>(d.peer_ag_arrive[r]);
       p.peer_slots[r] = reinterpret_cast<void*>(d.peer_slots[par][r]);
       p.peer_tile_flags[r] = reinterpret_cast<uint32_t*>(d.peer_tile_flags[r]);
       p.peer_res[r] = reinterpret_cast<void*>(d.peer_res[par][r]);
@@ -447,12 +458,27 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.prof = reinterpret_cast<uint64_t*>(d.prof);
     p.env.status = reinterpret_cast<StatusBlock*>(d.status_dev);
     p.env.abort_word = reinterpret_cast<uint32_t*>(d.abort_word);
+    p.env.n_peers = 0;
+    for (int r = 0; r < kMaxRanks; ++r) {
+      p.env.peer_abort[r] = reinterpret_cast<uint32_t*>(d.peer_abort[r]);
+      if (d.peer_abort[r] != 0) p.env.n_peers = static_cast<uint32_t>(r + 1);
+    }
     p.env.timeout_ns = d.timeout_ns;
     p.env.poll_ns = d.poll_ns;
     p.probe = (d.op == OP_PLAIN && d.R == 1) ? d.probe : 0;
     p.env.rank = static_cast<uint32_t>(d.rank);
   }
   plan->grid_x = grid_for(d, plan->prm[0], d.max_ctas, num_sms());
+  if (d.check_residency) {
+    const int fit = resident_ctas_of(*plan);
+    if (plan->grid_x > fit) {
+      const int gx = plan->grid_x;
+      delete plan;
+      throw std::runtime_error("tridist_b200: the kernel's " + std::to_string(gx) + " CTAs wait on one another but only " +
+                               std::to_string(fit) + " can be resident at once on this device (is another "
+                               "kernel holding SMs or shared memory?)");
+    }
+  }
   plan->prm[1].sk_tiles = plan->prm[0].sk_tiles;
   plan->prm[1].sk_slices = plan->prm[0].sk_slices;
   if (plan->prm[0].sk_tiles > 0) {
@@ -486,6 +512,51 @@ static GemmPlan* find_plan(int64_t id) {
   return it->second;
 }
 
+// CTAs of one variant that can be resident on the device at once (whole clusters for CTA pairs).
+// The kernels wait on one another across CTAs and across ranks, so a grid that does not fit in
+// one wave could wait for a CTA that is not running.
+template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
+static int resident_ctas() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  set_attr_once<BN, kBf16, kCtaM, kStaging, kMT>();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_sms() / kCtaM * kCtaM, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = TileShape<BN, kCtaM, kStaging, kMT>::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtaM;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  check(cudaOccupancyMaxActiveClusters(&clusters, fused_gemm_kernel<BN, kBf16, kCtaM, kStaging, kMT>, &cfg),
+        "cudaOccupancyMaxActiveClusters");
+  cached = clusters * kCtaM;
+  return cached;
+}
+
+static bool plan_uses_staging(const GemmParams& p) {
+  // operators that ship data to other ranks (epilogue tiles, all-gather push) need the staging area
+  return p.R > 1 && (p.op == OP_RS || p.op == OP_AR1 || p.op == OP_AR2 || p.op == OP_AG);
+}
+
+static int resident_ctas_of(const GemmPlan& plan) {
+  const bool st = plan_uses_staging(plan.prm[0]);
+#define TDB_RES(BN_, PAIR_, MT_)                                                            \
+  (plan.bf16 ? (st ? resident_ctas<BN_, true, PAIR_, true, MT_>() : resident_ctas<BN_, true, PAIR_, (MT_ == 2), MT_>()) \
+             : (st ? resident_ctas<BN_, false, PAIR_, true, MT_>() : resident_ctas<BN_, false, PAIR_, (MT_ == 2), MT_>()))
+  if (plan.bn == 256) {
+    if (plan.cta_m == 2 && plan.cta_mt == 2) return TDB_RES(256, 2, 2);
+    if (plan.cta_m == 2) return TDB_RES(256, 2, 1);
+    return TDB_RES(256, 1, 1);
+  }
+  return TDB_RES(128, 1, 1);
+#undef TDB_RES
+}
+
 template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
 static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
   set_attr_once<BN, kBf16, kCtaM, kStaging, kMT>();
@@ -506,18 +577,19 @@ static void launch_one(const GemmParams& p, int grid_x, cudaStream_t stream) {
         "fused_gemm_kernel launch");
 }
 
-void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm,
+void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int flags,
                       void* stream_) {
   GemmPlan* plan = find_plan(id);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   GemmParams& p = plan->prm[parity & 1];
   p.round = round;
   p.order_table = reinterpret_cast<const int32_t*>(order_table);
-  p.skip_comm = skip_comm & 1;
-  p.comm_only = (skip_comm >> 1) & 1;
+  p.table_has_header = (order_table != 0 && ((flags >> 3) & 1)) ? 1 : 0;
+  p.skip_comm = flags & 1;
+  p.comm_only = (flags >> 1) & 1;
+  p.publish_only = (flags >> 2) & 1;
   p.sk_epoch = ++g_sk_epoch;
-  // operators that ship data to other ranks (epilogue tiles, all-gather push) need the staging area
-  const bool staging = p.R > 1 && (p.op == OP_RS || p.op == OP_AR1 || p.op == OP_AR2 || p.op == OP_AG);
+  const bool staging = plan_uses_staging(p);
 #define TDB_LAUNCH(BN_, PAIR_)                                                              \
   do {                                                                                      \
     if (plan->bf16) {                                                                       \

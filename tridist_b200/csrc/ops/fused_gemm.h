@@ -30,7 +30,10 @@ struct GemmPlanDesc {
   int m_per_rank = 0;
   int seg_order[8] = {0, 1, 2, 3, 4, 5, 6, 7};
   int64_t order_table = 0;
+  int order_table_header = 0;   // order_table is part of a full skew table (see gemm_plan_launch, flag bit 3)
+  int check_residency = 0;      // refuse a plan whose grid cannot be resident in one wave (needs a device)
   int strided_interleave = 0;
+  int seg_bands = 0;        // SCHED_SEGMENT: row bands per segment walked band-major (0 / 1 = source-major)
   int seg_interleave = 0;   // SCHED_SEGMENT: all ranks walk the segments in lockstep (tile k of every segment, then k + 1)
   int64_t tile_list = 0;
   int list_len = 0;
@@ -43,6 +46,8 @@ struct GemmPlanDesc {
   // all-gather
   int64_t peer_ws[2][8] = {};
   int64_t peer_ag_flags[8] = {};
+  int64_t peer_ag_arrive[8] = {};   // pull transport: "source staged its chunk" tickets on every rank
+  int ag_pull = 0;
   int64_t ag_counters = 0;
   int64_t arrival_ns = 0;
   int chunk_rows = 0, n_chunks = 0, push_parts = 0, skip_comm = 0, push_ctas = 0, push_skip_rounds = 0;
@@ -62,12 +67,14 @@ struct GemmPlanDesc {
   // partial and result buffers; peer_slots then holds this rank's own partial buffer in every
   // entry and slot_stride is 0
   int nvls = 0;
+  int reduce_ctas = 0, reduce_tail = 0;   // reduce-scatter through the switch: steady CTA budget, tail window
   int64_t mc_part[2] = {};
   int64_t mc_res[2] = {};
   // failure reporting
   int64_t prof = 0;       // optional uint64 [grid][16] stall accounting (see ProfSlot)
   int64_t status_dev = 0;
   int64_t abort_word = 0;
+  int64_t peer_abort[8] = {};   // the abort word of every rank (raised together when one rank gives up)
   uint64_t timeout_ns = 2000000000ull;
   int probe = 0;          // pipeline probes of the plain GEMM (see GemmParams::probe)
   uint32_t poll_ns = 0;   // pause between two polls of a cross-rank flag
@@ -76,7 +83,10 @@ struct GemmPlanDesc {
 int64_t gemm_plan_create(const GemmPlanDesc& d);
 void gemm_plan_destroy(int64_t id);
 // `order_table`: optional device int32[R] overriding the segment order for this call.
-void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int skip_comm,
+// `flags`: bit 0 = no communication (GEMM only), bit 1 = communication only, bit 2 = publish
+// partial tiles but reduce nothing (all-reduce decomposition), bit 3 = order_table is the order[]
+// part of a full skew table (4 header words in front, R spin budgets behind).
+void gemm_plan_launch(int64_t id, uint32_t round, int parity, int64_t order_table, int flags,
                       void* stream);
 // Runs several ranks' plans as ONE cooperative kernel on one GPU (grid.y = rank).
 void gemm_plans_launch_emulated(const std::vector<int64_t>& ids, uint32_t round, int parity,

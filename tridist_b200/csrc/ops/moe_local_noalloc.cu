@@ -112,6 +112,7 @@ extern "C" int tdb_moe_local_dispatch_noalloc(const void* tokens, const int32_t*
   const int64_t pairs64 = static_cast<int64_t>(T) * topk;
   if (pairs64 >= (1ll << 31) || max_recv_rows < pairs64) return TDB_NOALLOC_EROWS;
   if (T > 0 && (!tokens || !recv)) return TDB_NOALLOC_ENULL;
+  if ((reinterpret_cast<uintptr_t>(tokens) | reinterpret_cast<uintptr_t>(recv)) & 15u) return TDB_NOALLOC_EALIGN;
   int32_t* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != TDB_NOALLOC_OK) return rc;
@@ -139,6 +140,7 @@ extern "C" const char* tdb_noalloc_strerror(int code) {
     case TDB_NOALLOC_EHIDDEN: return "hidden size must be a positive multiple of 8";
     case TDB_NOALLOC_EROWS: return "T * topk must be < 2^31 and recv must hold at least T * topk rows";
     case TDB_NOALLOC_ECUDA: return "a CUDA call failed (scratch symbol lookup or kernel launch)";
+    case TDB_NOALLOC_EALIGN: return "tokens and recv must start on 16-byte boundaries";
     default: return "unknown code";
   }
 }

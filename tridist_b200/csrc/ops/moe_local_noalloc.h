@@ -26,8 +26,13 @@
 //
 // Limits and rules
 //   * E <= TDB_NOALLOC_MAX_EXPERTS (1024), topk <= 32, H % 8 == 0, T * topk < 2^31,
-//     max_recv_rows >= T * topk. Anything else is refused with a negative return
-//     code before any kernel is launched; tdb_noalloc_strerror() names the reason.
+//     max_recv_rows >= T * topk; `tokens` and `recv` start on 16-byte boundaries (rows are
+//     moved with 16-byte loads and stores; a view at an odd offset is refused instead of
+//     faulting on the GPU). Anything else is refused with a negative return code before
+//     any kernel is launched; tdb_noalloc_strerror() names the reason.
+//   * `stream` must belong to the device that is current in the calling thread: the scratch
+//     address is looked up for the current device. The cached address does not outlive a
+//     cudaDeviceReset of that device.
 //   * The scratch is one file-scope device array of TDB_NOALLOC_SCRATCH_BYTES
 //     (8448 bytes) per GPU that loads this library; it stays resident until the
 //     process exits.
@@ -71,3 +76,4 @@ const char* tdb_noalloc_strerror(int code);
 #define TDB_NOALLOC_EHIDDEN (-4)     // H not a positive multiple of 8
 #define TDB_NOALLOC_EROWS (-5)       // T < 0, T * topk too large, or recv too small
 #define TDB_NOALLOC_ECUDA (-6)       // a CUDA call failed (symbol lookup or launch)
+#define TDB_NOALLOC_EALIGN (-7)      // tokens or recv does not start on a 16-byte boundary

@@ -55,6 +55,34 @@ def rotation_order(rank: int, R: int, step: int, own_last: bool) -> List[int]:
     return [(rank - i * step) % R for i in range(R)]
 
 
+MAX_TICKETS = 1 << 30
+
+
+def next_round(current: int, what: str = "context") -> int:
+    """The next monotonic ticket of a context. Tickets are 32-bit and compared by signed difference;
+    a context is refused long before that compare could wrap (the reference asserts a ticket
+    ceiling too, gemm_ar_rd.py:78,:422) and has to be created anew."""
+    nxt = current + 1
+    if nxt >= MAX_TICKETS:
+        raise RuntimeError(f"tridist_b200: this {what} has issued {current} tickets; create a new one "
+                           f"(tickets are 32-bit and must not wrap)")
+    return nxt
+
+
+_warned = set()
+
+
+def warn_ignored(where: str, **given) -> None:
+    """One warning per (entry point, argument) for a reference argument that has no counterpart in
+    the one-kernel design and was given a non-default value."""
+    import warnings
+    for name, (value, default) in given.items():
+        if value != default and (where, name) not in _warned:
+            _warned.add((where, name))
+            warnings.warn(f"tridist_b200.{where}: {name}={value!r} has no effect here "
+                          f"(kept for signature compatibility with the reference)", stacklevel=3)
+
+
 class PlanCache:
     def __init__(self, capacity: int = 64):
         self.capacity = capacity
@@ -127,7 +155,12 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
     d = dict(op=op, epi=EPI_STORE, sched=SCHED_NATURAL, bn=bn, bf16=is_bf16(a.dtype), rank=rank, R=R,
              M=M, N=N, K=K, a=a.data_ptr(), a_rows=a.shape[0], lda=a.stride(0),
              b=b.data_ptr(), b_rows=b.shape[0], ldb=b.stride(0), c=c_ptr, ldc=ldc,
-             status_dev=world.status_dev, abort_word=world.abort_word, timeout_ns=world.timeout_ns,
+             status_dev=world.status_dev,
+             abort_word=world.abort_word_of(rank) if hasattr(world, "abort_word_of") else world.abort_word,
+             peer_abort=world.peer_abort_words() if hasattr(world, "peer_abort_words") else [],
+             timeout_ns=world.timeout_ns,
+             # the grid must fit the device in one wave: its CTAs wait on one another
+             check_residency=1 if (env_int("TRIDIST_CHECK_RESIDENCY", 1) and getattr(world, "kind", "") != "emulated") else 0,
              max_ctas=env_int("TRIDIST_MAX_CTAS", 0) or
              (NUM_SMS_HINT // world.num_ranks if getattr(world, "kind", "") == "emulated" else 0),
              poll_ns=env_int("TRIDIST_POLL_NS", 0),

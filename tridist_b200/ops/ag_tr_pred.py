@@ -7,8 +7,12 @@ Public entry points of the reference's "I1" layer
 * ``i1_table_write(ictx, seq, deg, mode, order_packed, k_eff)``: publishes this forward's
   table ``[seq, degraded, mode, k_eff, order[R], budget[R]]`` (int32 words) to device memory
 * ``i1_ag_tr_op(a, b, c, ictx, stage_delay_us=0.0, with_observer=True)``: one AG+GEMM whose
-  consumer visits source segments in the table's order when ``mode == 1`` (predicted-early
-  sources first, predicted straggler last) and in the default arrival order otherwise
+  consumer reads the table on the device: ``mode == 1`` walks the source segments in the
+  table's order, source-major (predicted-early sources first, predicted straggler last);
+  ``mode == 0`` walks ``k_eff`` row bands band-major (band 0 of every source, then band 1, ...)
+  in the table's order; ``degraded == 1`` ignores the order and walks the default rotation
+  band-major; ``budget[s]`` is the number of polls of source s's ticket between two looks at
+  the abort word and the clock
 * ``i1_observer_read(ictx)``: ``[round, order by first-seen arrival..., arrival offsets in ns...]``
 * ``calibrate_sleep_cycles_per_us``
 
@@ -140,10 +144,9 @@ def i1_ag_tr_op(a, b, c, ictx, stage_delay_us: float = 0.0, with_observer: bool 
     ag.observe = bool(with_observer)
     if isinstance(ag.world, CpuWorld):
         return ag_gemm_intra_node_op(a, b, c, ag)
-    table = None
-    if ictx.mode == 1:
-        table = ictx.table[TABLE_HEADER_WORDS:TABLE_HEADER_WORDS + ag.num_ranks]
-    ag_gemm_intra_node_op(a, b, c, ag, order_table=table)
+    # the kernel reads the whole table: degraded / mode / k_eff in front of order[], budget[] behind
+    table = ictx.table[TABLE_HEADER_WORDS:TABLE_HEADER_WORDS + ag.num_ranks]
+    ag_gemm_intra_node_op(a, b, c, ag, order_table=table, table_header=True)
     ictx.last_round = ag.flag_round
     if env_flag("TRIDIST_VERIFY"):
         ictx.verify_hits += _verify_and_repair(a, b, c, ictx)

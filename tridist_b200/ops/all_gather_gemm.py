@@ -30,7 +30,7 @@ from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ..utils.config import env_int
-from ._gemm_common import (BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
+from ._gemm_common import (next_round, BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
                            base_desc, choose_bn, debug_check, rotation_order, tensor_extent_bytes)
 
 _CONSUMER_BLOCK_M = 128
@@ -49,7 +49,10 @@ class AllGatherGEMMTensorParallelContext:
     world: object
     ws: Optional[SymmBuffer] = None          # [2][max_M, K] gathered A, double-buffered
     flags: Optional[SymmBuffer] = None       # u32 [R, max_chunks] tickets, indexed by source
-    counters: Optional[torch.Tensor] = None  # local part counters of the push
+    arrive: Optional[SymmBuffer] = None      # u32 [R, max_chunks] "source staged its chunk" (pull transport)
+    transport: str = "push"                  # "push" | "pull"
+    push_ctas: int = 0                       # CTAs that carry the transfer (0 = chosen from the shape)
+    counters: Optional[torch.Tensor] = None  # local part counters of the transfer
     arrival_ns: Optional[torch.Tensor] = None  # int64 [R] first-seen arrival stamps (observer)
     flag_round: int = 0
     ag_stream: Optional[torch.cuda.Stream] = None
@@ -99,7 +102,8 @@ def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
     assert input_dtype == output_dtype, "the fused kernel emits the input dtype"
     ctx.ws = world.alloc(2 * max_M * K * 2, rank)
     ctx.flags = world.alloc(num_ranks * ctx.max_chunks * 4, rank)
-    ctx.counters = torch.zeros(num_ranks * ctx.max_chunks, dtype=torch.int32, device="cuda")
+    ctx.arrive = world.alloc(num_ranks * ctx.max_chunks * 4, rank)
+    ctx.counters = torch.zeros((num_ranks + 1) * ctx.max_chunks, dtype=torch.int32, device="cuda")
     ctx.arrival_ns = torch.zeros(num_ranks, dtype=torch.int64, device="cuda")
     world.host_barrier()
     return ctx
@@ -124,7 +128,7 @@ def _push_parts(chunk_rows: int, K: int) -> int:
     return parts
 
 
-def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int):
+def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int, want_ctas: int = 0):
     """(pushing CTAs, scheduling rounds they sit out). The pushing CTAs carry the whole shard to
     the peers before they compute anything; they skip as many rounds of tiles as that takes."""
     m_tiles = M // BM
@@ -137,6 +141,8 @@ def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int):
     tile_us = unit_rows * 256.0 * 2.0 * K / ((2 if pair else 1) * 8192.0 * 1500.0)
     out_bytes = (R - 1) * m_pr * K * 2.0
     forced_ctas, forced_skip = env_int("TRIDIST_PUSH_CTAS", -1), env_int("TRIDIST_PUSH_SKIP", -1)
+    if forced_ctas < 0 and want_ctas > 0:
+        forced_ctas = want_ctas
 
     def push_us(ctas: int) -> float:
         # measured: about 34 GB/s per pushing CTA (twelve 16 KB pieces in flight), 560 GB/s at most
@@ -174,7 +180,8 @@ def _plan(ctx, a, b, c, swiglu=False):
     baked_table = getattr(ctx, "emu_order_table", None)
     key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, K, a.stride(0), b.stride(0), c.stride(0),
            a.dtype, swiglu, bn, tuple(order), baked_table.data_ptr() if baked_table is not None else 0,
-           ctx.observe)
+           ctx.observe, getattr(ctx, "emu_table_header", False), getattr(ctx, "seg_bands", 0), ctx.transport,
+           ctx.push_ctas)
 
     def make():
         d = base_desc(ctx.world, rank, R, a, b, c.data_ptr(), c.stride(0), M, N, K, bn, OP_AG)
@@ -184,6 +191,8 @@ def _plan(ctx, a, b, c, swiglu=False):
         d["seg_order"] = order
         if baked_table is not None:
             d["order_table"] = baked_table.data_ptr()
+            d["order_table_header"] = 1 if getattr(ctx, "emu_table_header", False) else 0
+        d["seg_bands"] = int(getattr(ctx, "seg_bands", 0) or 0)
         if swiglu:
             d["epi"] = EPI_SWIGLU
             d["swiglu_up_row0"] = N
@@ -200,7 +209,11 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["push_parts"] = _push_parts(chunk, K)
             # A subset of the CTAs carries the push (their operand ring is the copy ring
             # meanwhile) and joins the GEMM as many rounds late as the push takes.
-            d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn)
+            d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn,
+                                                               ctx.push_ctas)
+            if ctx.transport == "pull":
+                d["ag_pull"] = 1
+                d["peer_ag_arrive"] = ctx.arrive.ptrs()
             debug_check(d, c_bytes=tensor_extent_bytes(c), ws_bytes=ctx.max_M * K * 2,
                         ag_flag_words=ctx.flags.nbytes // 4)
         else:
@@ -223,13 +236,16 @@ def _check_args(a, b, c, ctx):
 
 
 def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[torch.Tensor] = None,
-                          fuse_swiglu: bool = False, comm_only: bool = False):
+                          fuse_swiglu: bool = False, comm_only: bool = False, table_header: bool = False):
     """``c[M, N_pr] = allgather_M(a) @ b.T``.
 
     ``skip_comm=True`` is the GEMM-only decomposition mode: the kernel multiplies
     the workspace left by the last full call and pushes nothing.
     ``order_table`` (device int32[R]) overrides the source visiting order for this
-    call (skew-aware scheduling). ``fuse_swiglu`` treats b as ``[gate; up]`` and
+    call (skew-aware scheduling); with ``table_header=True`` it is the ``order[]`` part of a full
+    skew table ``[seq, degraded, mode, k_eff, order[R], budget[R]]`` and the kernel also honours
+    the mode (band-major / source-major walk), ``k_eff`` (row bands), ``degraded`` and the
+    per-source spin budgets. ``fuse_swiglu`` treats b as ``[gate; up]`` and
     writes ``silu(gate) * up`` (c has N_pr/2 columns). ``comm_only=True`` is the push-only
     decomposition mode: the shard is pushed and the tickets are raised, no tile is computed.
     """
@@ -237,7 +253,7 @@ def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[t
         return cpu_backend.ag_gemm(a, b, c, ctx, skip_comm, fuse_swiglu)
     _check_args(a, b, c, ctx)
     if not skip_comm:
-        ctx.flag_round += 1
+        ctx.flag_round = next_round(ctx.flag_round, "all-gather context")
     if ctx.flag_round == 0:
         raise RuntimeError("skip_comm=True needs a full call on this context first")
     if ctx.observe and not skip_comm:
@@ -245,7 +261,8 @@ def ag_gemm_intra_node_op(a, b, c, ctx, skip_comm=False, order_table: Optional[t
     pid = _plan(ctx, a, b, c, fuse_swiglu)
     native().gemm_plan_launch(pid, ctx.flag_round, ctx.flag_round & 1,
                               order_table.data_ptr() if order_table is not None else 0,
-                              (1 if skip_comm else 0) | (2 if comm_only else 0))
+                              (1 if skip_comm else 0) | (2 if comm_only else 0) |
+                              (8 if (table_header and order_table is not None) else 0))
     return c
 
 
@@ -265,7 +282,7 @@ def ag_gemm_emulated(ctxs, a_list, b_list, c_list, skip_comm=False, fuse_swiglu=
     for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list):
         _check_args(a, b, c, ctx)
         if not skip_comm:
-            ctx.flag_round += 1
+            ctx.flag_round = next_round(ctx.flag_round, "all-gather context")
     pids = [_plan(ctx, a, b, c, fuse_swiglu) for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list)]
     rnd = ctxs[0].flag_round
     flags = (1 if skip_comm else 0) | sum(1 << (8 + int(r)) for r in mute_ranks)
@@ -281,4 +298,6 @@ def finalize_ag_gemm_context(ctx) -> None:
     if not isinstance(ctx.world, EmulatedWorld):
         ctx.world.free(ctx.ws)
         ctx.world.free(ctx.flags)
-    ctx.ws = ctx.flags = None
+        if ctx.arrive is not None:
+            ctx.world.free(ctx.arrive)
+    ctx.ws = ctx.flags = ctx.arrive = None

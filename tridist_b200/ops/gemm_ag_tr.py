@@ -1,17 +1,22 @@
 """AG+GEMM, "tile-ready" entry points (reference: triton_dist/kernels/dcu/gemm_ag_tr.py:234-529).
 
 The reference re-designs its all-gather as a barrier-free, ticketed, chunk-major
-*pull* pipeline on several streams. On NVSwitch the base operator here already has
-those properties inside one kernel (monotonic tickets, no global barrier,
-double-buffered workspace), with push instead of pull, so these entry points keep
-the reference's names, argument lists and decomposition modes and run the same
-fused kernel. ``chunk_rows`` sets the ticket granularity; ``comm_lanes`` and
-``wait_mode`` are accepted and have no effect.
+*pull* pipeline on several streams: every rank stages its shard, tells the peers chunk
+by chunk that it is there ("arrive"), the peers copy it out and raise their own "ready"
+tickets for the consumer. The same transport runs here inside the one fused kernel
+(``transport="pull"``, the default of these entry points): the transfer CTAs stage,
+signal, pull through their copy engines and raise the ready tickets the producer warp
+waits on; ``transport="push"`` selects the base operator's push instead (one hop less).
+
+``chunk_rows`` sets the ticket granularity, ``comm_lanes`` the number of transfer CTAs
+(8 per lane; 2 lanes = the default of 16). ``wait_mode`` has no counterpart: every wait is
+an in-kernel bounded spin.
 """
 from __future__ import annotations
 
 import torch
 
+from ._gemm_common import warn_ignored
 from .all_gather_gemm import (ag_gemm_intra_node_op, create_ag_gemm_intra_node_context,
                               finalize_ag_gemm_context)
 
@@ -28,7 +33,7 @@ def _auto_chunk_rows(m_per_rank: int, target_chunks_per_rank: int = 2, min_chunk
 
 
 def create_gemm_ag_tr_context(max_M, K, input_dtype, output_dtype, rank, num_ranks, mpi=None, comm=None,
-                              chunk_rows=0, comm_lanes=2, wait_mode=None, world=None):
+                              chunk_rows=0, comm_lanes=2, wait_mode=None, world=None, transport="pull"):
     assert max_M % num_ranks == 0, "gather needs M % R == 0"
     m_pr = max_M // num_ranks
     assert K % 16 == 0 and input_dtype == output_dtype
@@ -38,6 +43,11 @@ def create_gemm_ag_tr_context(max_M, K, input_dtype, output_dtype, rank, num_ran
     ctx = create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank, num_ranks, mpi, comm,
                                             M_PER_CHUNK=rows, world=world)
     ctx.chunk_rows = rows
+    assert transport in ("pull", "push")
+    ctx.transport = transport
+    if comm_lanes != 2:
+        ctx.push_ctas = max(2, 8 * int(comm_lanes))
+    warn_ignored("create_gemm_ag_tr_context", wait_mode=(wait_mode, None))
     return ctx
 
 

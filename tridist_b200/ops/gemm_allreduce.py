@@ -44,7 +44,7 @@ from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ..utils.config import env_int, env_str
-from ._gemm_common import (BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_STRIDED, PlanCache,
+from ._gemm_common import (next_round, BM, OP_AR1, OP_AR2, OP_PLAIN, SCHED_STRIDED, PlanCache,
                            base_desc, choose_bn, debug_check, rotation_order, tensor_extent_bytes)
 
 
@@ -243,9 +243,10 @@ def gemm_ar_intra_node_op(a, b, c, ctx, component="full"):
     """``c[M, N] = sum over ranks of a @ b.T`` (replicated).
 
     ``component="gemm"`` runs the local GEMM only (partial result in c, no
-    communication); ``component="push"`` is accepted for the reference's
-    decomposition benches and runs the full fused kernel, since push and GEMM
-    are one kernel here.
+    communication); ``component="push"`` runs the GEMM and publishes the partial
+    tiles with their tickets but reduces nothing (c is left untouched) -- the
+    "GEMM + push" term of the reference's residue decomposition
+    (gemm_allreduce.py:330-338 there). With one rank both are the local GEMM.
     """
     if component not in ("full", "gemm", "push"):
         raise ValueError(f"unknown component {component!r}")
@@ -257,10 +258,11 @@ def gemm_ar_intra_node_op(a, b, c, ctx, component="full"):
     _check_args(a, b, c, ctx)
     mode = "gemm" if component == "gemm" else pick_mode(ctx, a.shape[0])
     if mode not in ("gemm", "local"):
-        ctx.flag_round += 1
+        ctx.flag_round = next_round(ctx.flag_round, "all-reduce context")
     rnd = max(ctx.flag_round, 1)
     pid = _plan(ctx, a, b, c, mode, rnd & 1)
-    native().gemm_plan_launch(pid, rnd, rnd & 1, 0, 0)
+    publish_only = component == "push" and mode not in ("gemm", "local")
+    native().gemm_plan_launch(pid, rnd, rnd & 1, 0, 4 if publish_only else 0)
     return c
 
 
@@ -278,7 +280,7 @@ def gemm_ar_intra_node(a, b, ctx):
 def gemm_ar_emulated(ctxs, a_list, b_list, c_list, mode="one_shot"):
     for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list):
         _check_args(a, b, c, ctx)
-        ctx.flag_round += 1
+        ctx.flag_round = next_round(ctx.flag_round, "all-reduce context")
     rnd = ctxs[0].flag_round
     pids = [_plan(ctx, a, b, c, mode, rnd & 1) for ctx, a, b, c in zip(ctxs, a_list, b_list, c_list)]
     native().gemm_plans_launch_emulated(pids, rnd, rnd & 1, 0)

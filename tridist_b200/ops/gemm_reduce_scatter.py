@@ -35,7 +35,7 @@ from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ..utils.config import env_int, env_str
-from ._gemm_common import (BM, OP_RS, SCHED_NATURAL, SCHED_SEGMENT, PlanCache, base_desc, choose_bn,
+from ._gemm_common import (next_round, BM, OP_RS, SCHED_NATURAL, SCHED_SEGMENT, PlanCache, base_desc, choose_bn,
                            debug_check, rotation_order, tensor_extent_bytes)
 
 
@@ -51,6 +51,8 @@ class GemmRSContext:
     tile_flags: Optional[SymmBuffer] = None  # u32 [R, max_tiles] tickets, by source
     mc: Optional[object] = None              # McBuffer [2][max_M, N]: this rank's partials, read through the switch
     mode: str = "auto"                       # "auto" | "slots" | "nvls"
+    reduce_ctas: int = 0                     # switch form: CTAs that reduce in the steady phase (0 = all)
+    reduce_tail: int = 0                     # switch form: last blocks that every CTA helps with
     round: int = 0
     plans: PlanCache = field(default_factory=PlanCache)
     order_override: Optional[list] = None
@@ -154,7 +156,7 @@ def _plan(ctx, a, b, out):
     # through the switch all ranks walk the same order (lockstep over the owners' segments)
     order = list(range(R)) if mode == "nvls" else (ctx.order_override or rotation_order(rank, R, 1, own_last=True))
     key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-           a.dtype, bn, tuple(order), mode)
+           a.dtype, bn, tuple(order), mode, ctx.reduce_ctas, ctx.reduce_tail)
 
     def make():
         d = base_desc(ctx.world, rank, R, a, b, out.data_ptr(), out.stride(0), M, N, K, bn, OP_RS)
@@ -172,6 +174,7 @@ def _plan(ctx, a, b, out):
                 d["peer_slots"] = [[ctx.mc.local_ptr] * R, [ctx.mc.local_ptr + half] * R]
                 d["slot_stride"] = 0
                 d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + half]
+                d["reduce_ctas"], d["reduce_tail"] = ctx.reduce_ctas, ctx.reduce_tail
             else:
                 d["peer_slots"] = [ctx.slots.ptrs(0), ctx.slots.ptrs(half)]
                 d["slot_stride"] = m_pr * N
@@ -202,7 +205,7 @@ def gemm_rs_intra_node_op(a, b, output_dtype, rank, num_ranks, ctx, out: Optiona
     M = a.shape[0]
     if out is None:
         out = torch.empty((M // num_ranks, b.shape[0]), dtype=output_dtype, device=a.device)
-    ctx.round += 1
+    ctx.round = next_round(ctx.round, "reduce-scatter context")
     pid = _plan(ctx, a, b, out)
     native().gemm_plan_launch(pid, ctx.round, ctx.round & 1, 0, 0)
     return out
@@ -216,7 +219,7 @@ def gemm_rs_emulated(ctxs, a_list, b_list):
     outs = []
     for ctx, a, b in zip(ctxs, a_list, b_list):
         _check_args(a, b, ctx)
-        ctx.round += 1
+        ctx.round = next_round(ctx.round, "reduce-scatter context")
         outs.append(torch.empty((a.shape[0] // ctx.num_ranks, b.shape[0]), dtype=a.dtype, device=a.device))
     pids = [_plan(ctx, a, b, o) for ctx, a, b, o in zip(ctxs, a_list, b_list, outs)]
     rnd = ctxs[0].round

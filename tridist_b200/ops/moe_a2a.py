@@ -23,6 +23,7 @@ from typing import List, Optional
 import torch
 
 from ..parallel import cpu_backend
+from ._gemm_common import next_round
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
 from ._gemm_common import is_bf16
@@ -129,7 +130,10 @@ def _desc(ctx, tokens=None, topk_idx=None, output=None, topk_weights=None, T=0):
              counters=ctx.counters.data_ptr(), recv_seg=ctx.recv_seg.data_ptr(),
              recv_counts=ctx.recv_counts.data_ptr(), recv_total=ctx.recv_total_t.data_ptr(),
              scatter_idx=ctx.scatter_idx.data_ptr(), done_counter=ctx.done_counter.data_ptr(),
-             status_dev=w.status_dev, abort_word=w.abort_word, timeout_ns=w.timeout_ns)
+             status_dev=w.status_dev,
+             abort_word=w.abort_word_of(ctx.rank) if hasattr(w, "abort_word_of") else w.abort_word,
+             peer_abort=w.peer_abort_words() if hasattr(w, "peer_abort_words") else [],
+             timeout_ns=w.timeout_ns)
     return d
 
 
@@ -150,7 +154,7 @@ def moe_dispatch_intra_node_op(tokens, topk_idx, ctx, component="full"):
     if isinstance(ctx.world, CpuWorld):
         return cpu_backend.moe_dispatch(tokens, topk_idx, ctx, component)
     T = _check_dispatch(tokens, topk_idx, ctx)
-    ctx.meta_round += 1
+    ctx.meta_round = next_round(ctx.meta_round, "MoE context")
     d = _desc(ctx, tokens=tokens, topk_idx=topk_idx, T=T)
     C = native()
     C.moe_meta(d)
@@ -176,7 +180,7 @@ def moe_dispatch_emulated(ctxs: List[MoEA2AContext], tokens_list, idx_list, comp
     ds = []
     for ctx, tok, idx in zip(ctxs, tokens_list, idx_list):
         T = _check_dispatch(tok, idx, ctx)
-        ctx.meta_round += 1
+        ctx.meta_round = next_round(ctx.meta_round, "MoE context")
         ds.append(_desc(ctx, tokens=tok, topk_idx=idx, T=T))
     C = native()
     C.moe_emulated(ds, 0)

@@ -38,11 +38,12 @@ class TriDistError(RuntimeError):
 SITE_NAMES = {
     1: "all-gather chunk ticket", 2: "reduce-scatter tile ticket", 3: "all-reduce tile ticket",
     4: "all-reduce result ticket", 5: "barrier", 6: "MoE metadata", 7: "MoE dispatch completion",
-    8: "MoE combine readiness", 9: "split-K partial", 16: "pipeline full barrier", 17: "pipeline empty barrier",
+    8: "MoE combine readiness", 9: "split-K partial", 10: "all-gather arrive ticket", 16: "pipeline full barrier", 17: "pipeline empty barrier",
     18: "TMEM full barrier", 19: "TMEM empty barrier", 32: "self test",
 }
 CODE_NAMES = {1: "flag wait timed out", 2: "pipeline barrier wait timed out",
-              3: "index out of range", 4: "receive buffer overflow"}
+              3: "index out of range", 4: "receive buffer overflow",
+              5: "gave up because another rank (or another role of the kernel) raised the abort word"}
 
 
 def native():
@@ -155,6 +156,15 @@ class ProcessWorld(_WorldBase):
         self.abort_buf = self.alloc(256)
         self.abort_word = self.abort_buf.local_ptr
         self.barrier_buf = self.alloc(256)
+
+    def abort_word_of(self, rank: int) -> int:
+        """The abort word the kernels of ``rank`` poll (this process runs one rank)."""
+        return self.abort_word
+
+    def peer_abort_words(self) -> List[int]:
+        """Every rank's abort word as addresses of this process: a kernel that gives up raises all
+        of them, so that the peers leave their waits at once."""
+        return list(self.abort_buf.peer_ptrs)
 
     # -- symmetric heap ------------------------------------------------------
     def alloc(self, nbytes: int, rank: Optional[int] = None) -> SymmBuffer:
@@ -271,7 +281,7 @@ class ProcessWorld(_WorldBase):
         if self.num_ranks == 1:
             return
         self.C.barrier_all(self.barrier_buf.ptrs(), self.rank, self.num_ranks, self._barrier_ticket,
-                           self.status_dev, self.abort_word, self.timeout_ns)
+                           self.status_dev, self.abort_word, self.timeout_ns, self.peer_abort_words())
 
     def host_barrier(self) -> None:
         torch.cuda.synchronize()
@@ -293,9 +303,11 @@ class ProcessWorld(_WorldBase):
                 f"(expected {expected}, saw {seen}, aux 0x{aux:x})")
 
     def clear_status(self) -> None:
+        """Forget a reported failure (every rank clears its own record and abort word)."""
         torch.cuda.synchronize()
         self.C.status_clear(self.status_host)
-        self.C.fill_u32(self.abort_word, 1, 0)
+        for r in range(self.num_ranks if self.kind == "emulated" else 1):
+            self.C.fill_u32(self.abort_word_of(r if self.kind == "emulated" else self.rank), 1, 0)
         torch.cuda.synchronize()
 
 
@@ -335,6 +347,13 @@ class EmulatedWorld(_WorldBase):
         base = self._shared[idx]
         assert base.nbytes == nbytes, "virtual ranks must allocate the same sizes in the same order"
         return self.view(base, rank)
+
+    def abort_word_of(self, rank: int) -> int:
+        """Every virtual rank polls its own word, as separate processes would."""
+        return self.abort_buf.peer_ptrs[rank]
+
+    def peer_abort_words(self) -> List[int]:
+        return list(self.abort_buf.peer_ptrs)
 
     def view(self, buf: SymmBuffer, rank: int) -> SymmBuffer:
         return SymmBuffer(nbytes=buf.nbytes, rank=rank, peer_ptrs=buf.peer_ptrs, device=buf.device,
