@@ -56,6 +56,21 @@ def _all_ops(rank, R):
             torch.cuda.synchronize()
             w.check()
             assert (c.float() - ref).abs().max().item() < TOL, f"AR {mode} round {it}"
+    # ---- decomposition: GEMM + publish without the reduce, then a full call again ----------
+    a_all, b_all = ks_inputs(R, M, N, kl, 77, dt)
+    a, b = a_all[rank].cuda(), b_all[rank].cuda()
+    ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
+    for mode in ("one_shot", "two_shot"):
+        ar.mode = mode
+        c = torch.full((M, N), 3.0, dtype=dt, device="cuda")
+        gemm_ar_intra_node_op(a, b, c, ar, component="push")
+        torch.cuda.synchronize()
+        w.check()
+        assert bool((c == 3.0).all()), "publish-only must not write the result"
+        gemm_ar_intra_node_op(a, b, c, ar)
+        torch.cuda.synchronize()
+        w.check()
+        assert (c.float() - ref).abs().max().item() < TOL, f"AR {mode} after a publish-only call"
     # ---- MoE ---------------------------------------------------------------
     E, H, topk, T = 8 * R, 1024, 4, 256
     moe = create_moe_a2a_intra_node_context(E, H, dt, T, topk, rank, R)
@@ -243,6 +258,9 @@ def _nvls_reduce_scatter(rank, R):
         rs.mode = "nvls"
         assert pick_mode(rs, max_M) == "nvls"
         for it, M in enumerate([max_M, max_M, max_M // 2, max_M // 4, max_M, max_M // 2]):
+            # the windowed entry points' reduce budget: 8 CTAs reduce while tiles are computed,
+            # every CTA helps with the last blocks (rounds 2 and 3)
+            rs.reduce_ctas, rs.reduce_tail = (8, 6) if it in (2, 3) else (0, 0)
             a_all, b_all = ks_inputs(R, M, N, kl, 40 + it, dt)
             ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
             out = gemm_rs_intra_node(a_all[rank].cuda(), b_all[rank].cuda(), rs)
@@ -268,3 +286,93 @@ def _nvls_reduce_scatter(rank, R):
 def test_nvls_reduce_scatter(R):
     from tridist_b200.utils.testing import spawn
     spawn(_nvls_reduce_scatter, R, backend="nccl", timeout=300)
+
+
+def _closed_loop_predictor(rank, R):
+    """observe -> table -> i1_ag_tr_op -> inferred straggler, on real ranks, with the straggler made
+    on the host (a sleep before its launch, after the ranks were aligned). Phase A: a sticky victim is
+    inferred by every other rank and moves to the end of their order (mode 1); the victim keeps the
+    rotation. Phase B: an alternating victim drives the stickiness below the threshold and the
+    table degrades. Every round's result is checked; explicit mode-0 and mode-1 tables give the same
+    bits."""
+    import time
+
+    import torch.distributed as dist
+    from tridist_b200.ops import (StickyOrderPredictor, create_i1_context, finalize_i1_context, i1_ag_tr_op,
+                                  i1_observer_read, i1_table_write, observed_straggler)
+    from tridist_b200.parallel.runtime import init_runtime
+    from tridist_b200.utils.testing import ag_inputs
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    w = init_runtime(rank, R)
+    dt = torch.float16
+    m_pr, K, n_pr = 512, 2048, 1024
+    ictx = create_i1_context(m_pr * R, K, dt, dt, rank, R, chunk_rows=256)
+    k_eff = 2
+    delay_s = 0.004
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def run_round(it, table, straggler):
+        a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, 500 + it, dt)
+        a, b = a_all[rank].cuda(), b.cuda()
+        c = torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda")
+        i1_table_write(ictx, table["seq"], table["degraded"], table["mode"], table["order_packed"], table["k_eff"])
+        torch.cuda.synchronize()
+        dist.barrier()                                   # aligned starts: the op-start skew is the sleep
+        if straggler is not None and rank == straggler:
+            time.sleep(delay_s)
+        e0.record()
+        i1_ag_tr_op(a, b, c, ictx)
+        e1.record()
+        torch.cuda.synchronize()
+        w.check()
+        ref = torch.cat(a_all, 0).cuda().float() @ b.float().t()
+        assert (c.float() - ref).abs().max().item() < TOL, f"round {it}"
+        return c, e0.elapsed_time(e1)
+
+    rot = sum(((rank + i) % R) << (4 * i) for i in range(R))
+    mode0 = dict(seq=1, degraded=0, mode=0, order_packed=rot, k_eff=k_eff)
+    mode1 = dict(seq=2, degraded=0, mode=1, order_packed=rot, k_eff=k_eff)
+    for it in range(2):
+        run_round(it, mode0, None)                       # warm-up
+    c0, _ = run_round(10, mode0, None)
+    c1, _ = run_round(10, mode1, None)                   # same data (same seed), other walk
+    assert torch.equal(c0, c1), "band-major and source-major walks must give the same bits"
+    base_ms = min(run_round(20 + j, mode0, None)[1] for j in range(3))
+
+    def infer(ms):
+        if R > 2:                                        # arrival stamps tell the late source apart
+            return observed_straggler(ictx)
+        return (1 - rank) if ms > base_ms * 1.6 + 1.0 else rank      # two ranks: my own round time
+
+    victim = 1
+    pred = StickyOrderPredictor(rank, R, window=4, stickiness_threshold=0.6)
+    modes = []
+    for it in range(5):
+        t = pred.table(k_eff=k_eff)
+        modes.append(t["mode"])
+        _, ms = run_round(100 + it, t, victim)
+        s_inf = infer(ms)
+        pred.observe(s_inf)
+        if rank != victim:
+            assert s_inf == victim, f"round {it}: inferred {s_inf} (ms {ms:.3f}, base {base_ms:.3f})"
+            assert i1_observer_read(ictx)[0] == ictx.last_round
+    if rank != victim:
+        assert modes[-1] == 1 and pred.last["order"][-1] == victim and pred.last["order"][0] == rank, pred.last
+    elif R == 2:
+        assert modes[-1] == 0                            # the victim sees no skew of its own: rotation
+    deg = False
+    for it in range(6):
+        t = pred.table(k_eff=k_eff)
+        deg |= bool(t["degraded"])
+        _, ms = run_round(200 + it, t, it % 2)
+        pred.observe(infer(ms))
+    if R == 2:
+        assert deg, pred.stats()
+    w.host_barrier()
+    finalize_i1_context(ictx)
+
+
+@pytest.mark.parametrize("R", [2, pytest.param(4, marks=_need(4))])
+def test_closed_loop_predictor_with_host_sleep_straggler(R):
+    from tridist_b200.utils.testing import spawn
+    spawn(_closed_loop_predictor, R, backend="nccl", timeout=600)
