@@ -197,6 +197,9 @@ def _nvls_all_reduce(rank, R):
     try:
         ar.mode = "nvls"
         assert pick_mode(ar, max_M) == "nvls"
+        # the buffer comes from this package's own allocator (cuMemCreate + cuMulticast*), not a fallback
+        if os.environ.get("TRIDIST_MC_ALLOC", "native") == "native":
+            assert getattr(w, "multicast_allocator", None) == "native", getattr(w, "multicast_native_unavailable", "")
         for it, M in enumerate([1024, 1024, 512, 128, 1024, 256]):
             a_all, b_all = ks_inputs(R, M, N, kl, it, dt)
             ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
@@ -226,7 +229,8 @@ def _nvls_all_reduce(rank, R):
         except Exception as exc:
             problems.append(f"release failed: {exc}")
     if rank == 0:
-        print("NVLS all-reduce:", "ok" if not problems else problems, flush=True)
+        print("NVLS all-reduce:", "ok" if not problems else problems, "| allocator:",
+              getattr(w, "multicast_allocator", None), getattr(w, "multicast_native_unavailable", ""), flush=True)
     assert not problems, problems
 
 

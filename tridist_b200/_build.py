@@ -26,6 +26,7 @@ _module = None
 SOURCES = [
     "bindings.cpp",
     "runtime/symm_heap.cu",
+    "runtime/vmm_heap.cu",
     "ops/fused_gemm.cu",
     "ops/elementwise.cu",
     "ops/moe_a2a.cu",

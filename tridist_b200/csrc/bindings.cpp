@@ -10,6 +10,7 @@
 #include "ops/moe_a2a.h"
 #include "common/status.h"
 #include "runtime/symm_heap.h"
+#include "runtime/vmm_heap.h"
 
 namespace py = pybind11;
 using namespace tdb;
@@ -205,6 +206,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_close", [](int64_t p) { symm_close_handle(reinterpret_cast<void*>(p)); });
   m.def("enable_peer_access", &symm_enable_peer_access);
   m.def("tensor_from_ptr", &tensor_from_ptr);
+
+  // ---- virtual-memory allocations and multicast objects ------------------------------
+  m.def("vmm_use_fake_driver", &vmm_use_fake_driver);
+  m.def("vmm_fake_call_log", &vmm_fake_call_log);
+  m.def("vmm_multicast_supported", [] {
+    std::string why;
+    const bool ok = vmm_multicast_supported(&why);
+    return std::make_pair(ok, why);
+  });
+  m.def("vmm_granularity", &vmm_granularity);
+  m.def("vmm_create", [](int64_t bytes) { return vmm_create(static_cast<size_t>(bytes)); });
+  m.def("vmm_export_fd", &vmm_export_fd);
+  m.def("vmm_import_fd", &vmm_import_fd);
+  m.def("vmm_map", [](int64_t h, int64_t bytes) { return reinterpret_cast<int64_t>(vmm_map(h, static_cast<size_t>(bytes))); });
+  m.def("vmm_unmap", [](int64_t p, int64_t bytes) { vmm_unmap(reinterpret_cast<void*>(p), static_cast<size_t>(bytes)); });
+  m.def("vmm_release", &vmm_release);
+  m.def("vmm_mc_create", [](int64_t bytes, int n) { return vmm_mc_create(static_cast<size_t>(bytes), n); });
+  m.def("vmm_mc_add_device", &vmm_mc_add_device);
+  m.def("vmm_mc_bind", [](int64_t mc, int64_t mem, int64_t bytes) { vmm_mc_bind(mc, mem, static_cast<size_t>(bytes)); });
+  m.def("vmm_mc_unbind", [](int64_t mc, int64_t bytes) { vmm_mc_unbind(mc, static_cast<size_t>(bytes)); });
 
   // ---- status plane -----------------------------------------------------------
   m.def("status_alloc", [] {

@@ -25,7 +25,7 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from ..utils.config import env_int
+from ..utils.config import env_int, env_str
 
 _DTYPE_SIZE = {torch.float16: 2, torch.bfloat16: 2, torch.float32: 4, torch.int32: 4,
                torch.int64: 8, torch.uint8: 1}
@@ -124,6 +124,30 @@ class _WorldBase:
     def free_multicast(self, buf) -> None:
         return None
 
+    def _alloc_multicast_native(self, nbytes: int) -> Optional["McBuffer"]:
+        """Collective. The package's own allocator (cuMemCreate / POSIX descriptors / cuMulticast*,
+        ``parallel/vmm.py``); None on every rank when any rank cannot have it."""
+        from . import vmm
+        ok, why = self.C.vmm_multicast_supported()
+        oks = [None] * self.num_ranks
+        dist.all_gather_object(oks, "" if ok else (why or "multicast not supported"), group=self.group)
+        if any(oks):
+            self.multicast_native_unavailable = "; ".join(f"rank {r}: {w}" for r, w in enumerate(oks) if w)
+            return None
+        try:
+            alloc = vmm.alloc_symmetric_multicast(self.C, self.rank, self.num_ranks, self.group, nbytes)
+        except RuntimeError as exc:                  # the same on every rank
+            self.multicast_native_unavailable = str(exc)
+            return None
+        buf = McBuffer(nbytes=alloc.nbytes, rank=self.rank, peer_ptrs=list(alloc.peer_ptrs), device=self.device,
+                       _owner=self, mc_ptr=alloc.mc_ptr, _keep=alloc)
+        self.multicast_allocator = "native"
+        self.C.fill_u32(buf.local_ptr, alloc.nbytes // 4, 0)     # driver allocations are not zeroed
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._mc_buffers.append(buf)
+        return buf
+
     def release_multicast(self) -> None:
         return None
 
@@ -217,6 +241,11 @@ class ProcessWorld(_WorldBase):
         no multicast support in the driver / fabric, or a failed rendezvous."""
         if self.num_ranks < 2 or env_int("TRIDIST_NVLS", 1) == 0:
             return None
+        if env_str("TRIDIST_MC_ALLOC", "native") == "native":
+            buf = self._alloc_multicast_native(nbytes)
+            if buf is not None:
+                return buf
+            # (every rank took the same branch: the outcome of the native attempt is agreed)
         tensor = handle = None
         mc, ptrs, why = 0, [], ""
         group = self.group if self.group is not None else dist.group.WORLD
@@ -251,8 +280,33 @@ class ProcessWorld(_WorldBase):
             self.multicast_unavailable = "; ".join(f"rank {r}: {w}" for r, w in enumerate(oks) if w)
             del handle, tensor
             return None
+        self.multicast_allocator = "torch"
         buf = McBuffer(nbytes=nbytes, rank=self.rank, peer_ptrs=ptrs, device=self.device, _owner=self,
                        mc_ptr=mc, _keep=(tensor, handle))
+        self._mc_buffers.append(buf)
+        return buf
+
+    def _alloc_multicast_native(self, nbytes: int) -> Optional["McBuffer"]:
+        """Collective. The package's own allocator (cuMemCreate / POSIX descriptors / cuMulticast*,
+        ``parallel/vmm.py``); None on every rank when any rank cannot have it."""
+        from . import vmm
+        ok, why = self.C.vmm_multicast_supported()
+        oks = [None] * self.num_ranks
+        dist.all_gather_object(oks, "" if ok else (why or "multicast not supported"), group=self.group)
+        if any(oks):
+            self.multicast_native_unavailable = "; ".join(f"rank {r}: {w}" for r, w in enumerate(oks) if w)
+            return None
+        try:
+            alloc = vmm.alloc_symmetric_multicast(self.C, self.rank, self.num_ranks, self.group, nbytes)
+        except RuntimeError as exc:                  # the same on every rank
+            self.multicast_native_unavailable = str(exc)
+            return None
+        buf = McBuffer(nbytes=alloc.nbytes, rank=self.rank, peer_ptrs=list(alloc.peer_ptrs), device=self.device,
+                       _owner=self, mc_ptr=alloc.mc_ptr, _keep=alloc)
+        self.multicast_allocator = "native"
+        self.C.fill_u32(buf.local_ptr, alloc.nbytes // 4, 0)     # driver allocations are not zeroed
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
         self._mc_buffers.append(buf)
         return buf
 
@@ -268,6 +322,9 @@ class ProcessWorld(_WorldBase):
             return
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
+        from . import vmm
+        if isinstance(buf._keep, vmm.VmmAllocation):
+            vmm.free_symmetric_multicast(self.C, self.group, buf._keep, self.num_ranks)
         buf._keep = None
         buf.freed = True
         if buf in self._mc_buffers:
