@@ -131,7 +131,15 @@ moe_dispatch_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restric
     const int dest = e / d.epr;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(d.tokens) + t * row_bytes;
     uint8_t* dst = reinterpret_cast<uint8_t*>(d.peer_recv[dest]) + row * row_bytes;
+    // eight 16-byte pieces per lane in flight (4 KB per warp): a row of 8 KB is two such batches
     int i = lane;
+    for (; i + 224 < n16; i += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = ld_global_nc_v4(src + ((i + 32 * u) << 4));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) st_global_v4(dst + ((i + 32 * u) << 4), v[u]);
+    }
     for (; i + 96 < n16; i += 128) {
       uint4 v[4];
 #pragma unroll
@@ -230,16 +238,16 @@ moe_combine_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restrict
     __syncthreads();
     for (int v = tid; v < n16; v += blockDim.x) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j0 = 0; j0 < d.topk; j0 += 4) {
-        uint4 val[4];
+      for (int j0 = 0; j0 < d.topk; j0 += 8) {
+        uint4 val[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const int j = j0 + u;
           val[u] = (j < d.topk && s_src[j] != nullptr) ? ld_global_cg_v4(s_src[j] + (v << 4))
                                                        : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           if (j0 + u < d.topk) fma8<kBf16>(acc, val[u], s_w[j0 + u]);
       }
       st_global_v4(reinterpret_cast<uint8_t*>(d.output) + t * row_bytes + (v << 4), pack8<kBf16>(acc));
