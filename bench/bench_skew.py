@@ -14,6 +14,17 @@ For every delta the script reports the mean device time of the op on the non-vic
 the least-squares slope of time against delta per arm (1.0 = the delay is fully exposed,
 0 = fully absorbed), and the predictor statistics. Injection is host-side sleep only.
 
+Pass criteria, fixed before any run (in the spirit of the reference's pre-registered gates,
+bench/l1_pred_aggregate.py C1-C5 and bench/s20_bench_8card.py G1-G3); the report carries one
+verdict per criterion under "criteria":
+
+  C1  no harm without skew: pred at delta = 0 is within 3 % (or 10 us) of nopred
+  C2  the prediction helps: slope(pred) <= slope(nopred) - 0.03 when more than two ranks take
+      part (with two ranks there is no order to choose, the criterion is recorded as "n/a")
+  C3  the predictor finds the victim: degrade rate of the pred arm <= 0.25 over all rounds with skew
+  C4  the oracle bounds the predictor: slope(pred) >= slope(oracle) - 0.10
+  C5  correctness: the first and the last result of every arm match the fp32 reference on a row sample
+
   python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench/bench_skew.py \
       --m-per-rank 1024 --k 8192 --n-per-rank 3584 --deltas 0,100,200,400,800 --victim 3
 """
@@ -70,7 +81,14 @@ def main():
     c = torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda")
     ictx = create_i1_context(m_pr * R, K, dt, dt, rank, R)
     deltas = [float(x) for x in args.deltas.split(",")]
-    report = {"config": vars(args), "ranks": R, "arms": {}}
+    cfg = dict(vars(args))
+    cfg.pop("out", None)                      # where the report goes is not part of the experiment
+    report = {"config": cfg, "ranks": R, "arms": {}}
+    rows = torch.arange(0, m_pr * R, max(1, (m_pr * R) // 64), device="cuda")[:64]
+    a_all = [torch.empty_like(a) for _ in range(R)]
+    dist.all_gather(a_all, a)
+    ref_rows = torch.cat(a_all, 0)[rows].float() @ b.float().t()
+    correct = True
 
     def pack(order):
         return sum(int(o) << (4 * i) for i, o in enumerate(order))
@@ -98,6 +116,8 @@ def main():
                 e1.record()
                 torch.cuda.synchronize()
                 rt.check()
+                if rnd in (0, args.rounds - 1):
+                    correct &= bool((c[rows].float() - ref_rows).abs().max().item() < 2e-2)
                 if arm == "pred":
                     pred.observe(observed_straggler(ictx) if delta > 0 else None)
                 if rnd >= 4:                                    # first rounds warm the predictor
@@ -113,6 +133,21 @@ def main():
                                "predictor": stats}
         if rank == 0:
             print(arm, json.dumps(report["arms"][arm]), flush=True)
+    ok_all = torch.tensor([1.0 if correct else 0.0], device="cuda")
+    dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+    arms = report["arms"]
+    z = str(deltas[0])
+    t0_pred, t0_no = arms["pred"]["mean_ms_non_victim"][z], arms["nopred"]["mean_ms_non_victim"][z]
+    s_pred, s_no, s_or = (arms[k]["slope_ms_per_ms"] for k in ("pred", "nopred", "oracle"))
+    report["criteria"] = {
+        "C1_no_harm_at_zero_delay": bool(deltas[0] != 0 or t0_pred <= max(t0_no * 1.03, t0_no + 0.010)),
+        "C2_prediction_helps": (bool(s_pred <= s_no - 0.03) if R > 2 else "n/a"),
+        "C3_victim_found": bool((arms["pred"]["predictor"] or {}).get("degrade_rate", 1.0) <= 0.25),
+        "C4_oracle_bounds_predictor": bool(s_pred >= s_or - 0.10),
+        "C5_results_correct": bool(ok_all.item() > 0),
+    }
+    if rank == 0:
+        print("criteria", json.dumps(report["criteria"]), flush=True)
     if rank == 0 and args.out:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
         with open(args.out, "w") as fh:

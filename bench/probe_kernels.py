@@ -4,6 +4,7 @@ quick event-timed bandwidth / throughput read-out without a profiler.
 
   python bench/probe_kernels.py --what ag_emulated      two virtual ranks, fused all-gather + GEMM
   python bench/probe_kernels.py --what rs_emulated      two virtual ranks, fused GEMM + reduce-scatter
+  python bench/probe_kernels.py --what ar_emulated      two virtual ranks, fused GEMM + two-shot all-reduce
   python bench/probe_kernels.py --what moe              metadata + dispatch + combine (one rank)
   python bench/probe_kernels.py --what swiglu           stand-alone SwiGLU
   python bench/probe_kernels.py --what all
@@ -39,7 +40,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="all")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--pairs", type=int, default=1, help="1: the virtual ranks run CTA pairs with 512-row tiles "
+                    "(the production tile shape), 0: single-CTA 128 x 256 tiles")
     args = ap.parse_args()
+    os.environ["TRIDIST_EMU_PAIR"] = str(args.pairs)
     import torch
     from tridist_b200.parallel.runtime import EmulatedWorld, ProcessWorld
     from tridist_b200.utils.roofline import load_peaks
@@ -58,7 +62,7 @@ def main():
         ms = timed(lambda: ag_gemm_emulated(ctxs, a, b, c), args.iters)
         w.check(sync=True)
         flops = R * 2.0 * (m_pr * R) * n_pr * K
-        print(json.dumps({"kernel": "fused_gemm_kernel (AG, 2 virtual ranks, 74 CTAs each)", "ms": round(ms, 4),
+        print(json.dumps({"kernel": "fused_gemm_kernel (AG, 2 virtual ranks)", "ms": round(ms, 4),
                           "tflops": round(flops / ms / 1e9, 1)}))
 
     if what in ("rs_emulated", "all"):
@@ -71,7 +75,21 @@ def main():
         ms = timed(lambda: gemm_rs_emulated(ctxs, a, b), args.iters)
         w.check(sync=True)
         flops = R * 2.0 * M * N * kl
-        print(json.dumps({"kernel": "fused_gemm_kernel (RS, 2 virtual ranks, 74 CTAs each)", "ms": round(ms, 4),
+        print(json.dumps({"kernel": "fused_gemm_kernel (RS, 2 virtual ranks)", "ms": round(ms, 4),
+                          "tflops": round(flops / ms / 1e9, 1)}))
+
+    if what in ("ar_emulated", "all"):
+        from tridist_b200.ops.gemm_allreduce import create_gemm_ar_intra_node_context, gemm_ar_emulated
+        R, M, N, kl = 2, 4096, 4096, 4096
+        w = EmulatedWorld(R)
+        ctxs = [create_gemm_ar_intra_node_context(M, N, dt, dt, r, R, M_PER_CHUNK=64, world=w) for r in range(R)]
+        a = [(torch.randn(M, kl, device="cuda") * 0.05).to(dt) for _ in range(R)]
+        b = [(torch.randn(N, kl, device="cuda") * 0.05).to(dt) for _ in range(R)]
+        c = [torch.empty(M, N, dtype=dt, device="cuda") for _ in range(R)]
+        ms = timed(lambda: gemm_ar_emulated(ctxs, a, b, c, mode="two_shot"), args.iters)
+        w.check(sync=True)
+        flops = R * 2.0 * M * N * kl
+        print(json.dumps({"kernel": "fused_gemm_kernel (two-shot AR, 2 virtual ranks)", "ms": round(ms, 4),
                           "tflops": round(flops / ms / 1e9, 1)}))
 
     if what in ("moe", "all"):

@@ -664,3 +664,30 @@ def test_band_major_schedule_walks_bands_first():
         if not walk or walk[-1] != key:
             walk.append(key)
     assert walk == [(s, b) for b in range(2) for s in [1, 0, 3, 2]]
+
+
+def test_device_side_index_check_reports_and_skips():
+    """A row index outside the receive buffer (made here by damaging the scatter table between dispatch
+    and combine) is recorded as 'index out of range' and the access is skipped: nothing faults."""
+    from tridist_b200.ops import (create_moe_a2a_intra_node_context, moe_combine_intra_node_op,
+                                  moe_dispatch_intra_node_op)
+    from tridist_b200.parallel.runtime import TriDistError
+    from tridist_b200.utils.testing import moe_inputs
+    w = _world1()
+    w.clear_status()
+    dt = torch.float16
+    E, H, topk, T = 8, 256, 2, 64
+    ctx = create_moe_a2a_intra_node_context(E, H, dt, T, topk, 0, 1, world=w)
+    tokens, idx, wts = [x.cuda() for x in moe_inputs(0, T, H, E, topk, 3, dt)]
+    moe_dispatch_intra_node_op(tokens, idx, ctx)
+    ctx.out[:T * topk] = ctx.recv[:T * topk]
+    ctx.scatter_idx[5, 1] = ctx.recv.shape[0] + 17
+    out = torch.empty_like(tokens)
+    moe_combine_intra_node_op(ctx, idx, out, wts)
+    torch.cuda.synchronize()
+    st = w.status()
+    assert st[0] == 3 and st[2] == 11 and st[4] == ctx.recv.shape[0] + 17
+    with pytest.raises(TriDistError, match="index out of range"):
+        w.check()
+    w.clear_status()
+    assert bool(torch.isfinite(out.float()).all())

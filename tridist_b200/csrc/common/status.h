@@ -8,7 +8,7 @@ enum StatusCode : uint32_t {
   ST_OK = 0,
   ST_TIMEOUT_FLAG = 1,     // a cross-rank flag did not reach its ticket in time
   ST_TIMEOUT_MBAR = 2,     // an intra-CTA pipeline barrier did not flip in time
-  ST_BAD_INDEX = 3,        // a computed row / tile / offset was out of range
+  ST_BAD_INDEX = 3,        // a computed row / tile / ticket index failed its range check; the access was skipped
   ST_OVERFLOW = 4,         // a receive buffer would be oversubscribed
   ST_PEER_ABORT = 5,       // a wait was abandoned because another role or another rank gave up first
 };
@@ -24,7 +24,8 @@ enum WaitSite : uint32_t {
   SITE_MOE_DISPATCH_DONE = 7,
   SITE_MOE_COMBINE_READY = 8,
   SITE_SPLITK = 9,
-  SITE_AG_ARRIVE = 10,     // pull all-gather: waiting for a source to stage its chunk         // split-K finisher waiting for another slice's partial
+  SITE_AG_ARRIVE = 10,
+  SITE_INDEX_CHECK = 11,   // a computed ticket / row / chunk index failed its range check (nothing was accessed)     // pull all-gather: waiting for a source to stage its chunk         // split-K finisher waiting for another slice's partial
   SITE_PIPE_FULL = 16,
   SITE_PIPE_EMPTY = 17,
   SITE_TMEM_FULL = 18,

@@ -688,6 +688,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               const int r_hi = min(r_lo + kMT * BM, p.m_per_rank) - 1;
               for (int ck = r_lo / p.chunk_rows; ok && ck <= r_hi / p.chunk_rows; ++ck) {
                 if (ck < 32 && (ready_mask[src] >> ck) & 1u) continue;
+                if (src < 0 || src >= p.R || ck >= p.ag_flag_stride) {     // never index a ticket plane blindly
+                  report_failure(env, ST_BAD_INDEX, SITE_INDEX_CHECK, static_cast<uint32_t>(p.ag_flag_stride),
+                                 static_cast<uint32_t>(ck), static_cast<uint32_t>(src));
+                  ok = false;
+                  break;
+                }
                 const uint32_t* f = p.peer_ag_flags[p.rank] + src * p.ag_flag_stride + ck;
                 const uint64_t tw = prof ? globaltimer_ns() : 0;
                 ok = wait_flag_ge(f, p.round, env, SITE_AG_CHUNK, (src << 16) | ck,
@@ -1084,6 +1090,16 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         }
       }
       if (p.publish_only) tile_reduces = false;     // decomposition mode: publish and ticket, no reduce
+      // Range check of the indices every later access of this block derives from (the plan was
+      // checked on the host, the table-driven orders and the peers' shapes were not): a bad one
+      // is recorded and nothing is accessed with it.
+      if (multi && tile_has_rows && (tile_publishes || tile_reduces) &&
+          (lin < 0 || lin >= tiles || owner < 0 || owner >= p.R)) {
+        if (etid == 0) report_failure(env, ST_BAD_INDEX, SITE_INDEX_CHECK, static_cast<uint32_t>(tiles),
+                                      static_cast<uint32_t>(lin), static_cast<uint32_t>(m_tile));
+        alive = false;
+        break;
+      }
       // the accumulator is needed after the publish phase only where this rank adds the
       // peers' partials to it (its own rows of a reduce-scatter tile)
       const bool acc_needed_later = tile_reduces && p.op == OP_RS;

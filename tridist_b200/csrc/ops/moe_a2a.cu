@@ -119,7 +119,11 @@ moe_dispatch_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restric
       if (e >= 0 && e < d.E) {
         const int slot = atomicAdd(&d.counters[e], 1);
         row = d.dst_row_base[e] + slot;
-        if (row >= d.max_recv_rows) {
+        if (row < 0) {
+          // the base comes from counts other ranks wrote: a negative row is recorded, never used
+          report_failure(d.env, ST_BAD_INDEX, SITE_INDEX_CHECK, 0u, static_cast<uint32_t>(row), e);
+          row = -1;
+        } else if (row >= d.max_recv_rows) {
           report_failure(d.env, ST_OVERFLOW, SITE_MOE_DISPATCH_DONE, d.max_recv_rows, row, e);
           row = -1;
         }
@@ -231,6 +235,9 @@ moe_combine_kernel(const __grid_constant__ MoeDesc d0, const MoeDesc* __restrict
       const int e = d.topk_idx[pair];
       const int row = d.scatter_idx[pair];
       const bool valid = (e >= 0 && e < d.E && row >= 0 && row < d.max_recv_rows);
+      if (e >= 0 && e < d.E && (row < -1 || row >= d.max_recv_rows))      // -1 = dropped at dispatch
+        report_failure(d.env, ST_BAD_INDEX, SITE_INDEX_CHECK, static_cast<uint32_t>(d.max_recv_rows),
+                       static_cast<uint32_t>(row), e);
       s_src[tid] = valid ? reinterpret_cast<const uint8_t*>(d.peer_out[e / d.epr]) + row * row_bytes
                          : nullptr;
       s_w[tid] = d.has_weights ? d.topk_weights[pair] : 1.0f;
