@@ -127,6 +127,7 @@ def _multicast_one_rank_cannot(rank, R, outdir):
             raise AssertionError("rendezvous entered although a rank could not allocate")
 
     runtime._symm_mem_module = lambda: FakeSymm
+    os.environ["TRIDIST_MC_ALLOC"] = "torch"                    # the path through torch's allocator
     w = runtime.ProcessWorld.__new__(runtime.ProcessWorld)      # host logic only: no device, no heap
     runtime._WorldBase.__init__(w)
     w.rank, w.num_ranks, w.group, w.device = rank, R, None, 0
