@@ -29,14 +29,19 @@ def is_bf16(dtype: torch.dtype) -> bool:
     raise TypeError(f"tridist_b200: fused GEMM kernels support fp16 and bf16, got {dtype}")
 
 
-def choose_bn(M: int, N: int, swiglu: bool = False) -> int:
-    """Output-tile width: 256 unless that leaves most SMs without a tile."""
+def choose_bn(M: int, N: int, swiglu: bool = False, K: int = 0) -> int:
+    """Output-tile width: 256 unless that leaves most SMs without a tile. A single row block
+    (M <= 128) with a long K is the exception: every CTA re-reads the whole A slice of its K
+    range, so wider tiles (fewer CTAs per K range, more K slices instead) move a quarter less
+    through the L2 fabric, which is what bounds that shape."""
     if swiglu:
         return 256       # gate and up halves are two 128-row TMA boxes of one 256-wide tile
     forced = env_int("TRIDIST_FORCE_BN", 0)
     if forced in (128, 256):
         return forced
     m_tiles = (M + BM - 1) // BM
+    if m_tiles == 1 and K >= 8192 and N >= 2048:
+        return 256
     width = 128 if swiglu else 256           # output columns covered by a BN=256 tile
     tiles256 = m_tiles * ((N + width - 1) // width)
     return 256 if tiles256 >= NUM_SMS_HINT - 28 else 128
@@ -236,7 +241,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         out = torch.empty((M, N), dtype=a.dtype, device=a.device)
     assert out.stride(1) == 1
     if bn is None:
-        bn = choose_bn(M, N, swiglu)
+        bn = choose_bn(M, N, swiglu, K=K)
     w = plain_world()
     key = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
            out.stride(0), bn, swiglu, a.dtype, max_ctas, probe)

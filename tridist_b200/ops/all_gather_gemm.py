@@ -174,7 +174,7 @@ def _plan(ctx, a, b, c, swiglu=False):
     M = m_pr * R
     n_rows = b.shape[0]
     N = n_rows // 2 if swiglu else n_rows
-    bn = choose_bn(M, N, swiglu)
+    bn = choose_bn(M, N, swiglu, K=K)
     order = ctx.order_override or rotation_order(rank, R, 1, own_last=False)
     # emulated launches cannot take a per-call table: a device order table is baked into the plan
     baked_table = getattr(ctx, "emu_order_table", None)

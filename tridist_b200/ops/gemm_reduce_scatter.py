@@ -151,7 +151,7 @@ def _plan(ctx, a, b, out):
     M, K = a.shape
     N = b.shape[0]
     m_pr = M // R
-    bn = choose_bn(M, N)
+    bn = choose_bn(M, N, K=K)
     mode = pick_mode(ctx, M)
     # through the switch all ranks walk the same order (lockstep over the owners' segments)
     order = list(range(R)) if mode == "nvls" else (ctx.order_override or rotation_order(rank, R, 1, own_last=True))
