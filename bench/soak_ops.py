@@ -55,7 +55,7 @@ def soak(rank: int, R: int, world, rounds: int, small: bool, dtype, tol: float, 
         ctx = create_ag_gemm_intra_node_context(m_pr * R, K, dtype, dtype, rank, R, M_PER_CHUNK=m_pr, world=world)
         c = torch.empty(m_pr * R, n_pr, dtype=dtype, device=dev)
         for rnd in range(rounds):
-            a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, rnd, dtype)
+            a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, rnd, dtype, device=dev)
             ag_gemm_intra_node_op(a_all[rank].to(dev), b.to(dev), c, ctx)
             sync()
             world.check()
@@ -70,7 +70,7 @@ def soak(rank: int, R: int, world, rounds: int, small: bool, dtype, tol: float, 
         c = torch.empty(M, N, dtype=dtype, device=dev)
         m_pr = M // R
         for rnd in range(rounds):
-            a_all, b_all = ks_inputs(R, M, N, kl, rnd, dtype)
+            a_all, b_all = ks_inputs(R, M, N, kl, rnd, dtype, device=dev)
             ref = sum(a_all[s].to(dev).float() @ b_all[s].to(dev).float().t() for s in range(R))
             a, b = a_all[rank].to(dev), b_all[rank].to(dev)
             if rs is not None:

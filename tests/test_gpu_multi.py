@@ -17,7 +17,8 @@ TOL = 1e-2
 def _all_ops(rank, R):
     from tridist_b200.ops import (ag_gemm_intra_node_op, create_ag_gemm_intra_node_context,
                                   create_gemm_ar_intra_node_context, create_gemm_rs_intra_node_context,
-                                  create_moe_a2a_intra_node_context, gemm_ar_intra_node_op, gemm_rs_intra_node,
+                                  create_moe_a2a_intra_node_context, finalize_ag_gemm_context,
+                                  gemm_ar_intra_node_op, gemm_rs_intra_node,
                                   moe_combine_intra_node_op, moe_dispatch_intra_node_op)
     from tridist_b200.parallel.runtime import init_runtime
     from tridist_b200.utils.testing import ag_inputs, fake_expert, ks_inputs, moe_inputs
@@ -26,16 +27,21 @@ def _all_ops(rank, R):
     dt = torch.float16
     # ---- AG + GEMM ---------------------------------------------------------
     m_pr, K, n_pr = 512, 1024, 768
-    ctx = create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, rank, R, M_PER_CHUNK=256)
-    for it in range(4):
-        a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, it, dt)
-        a, b = a_all[rank].cuda(), b.cuda()
-        c = torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda")
-        ag_gemm_intra_node_op(a, b, c, ctx)
-        torch.cuda.synchronize()
-        w.check()
-        ref = torch.cat(a_all, 0).cuda().float() @ b.float().t()
-        assert (c.float() - ref).abs().max().item() < TOL, f"AG round {it}"
+    # every transport: multicast stores through the switch (what "auto" picks where the fabric has
+    # multicast), bulk-copy push, pull
+    for transport in ("auto", "push", "pull"):
+        ctx = create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, rank, R, M_PER_CHUNK=256, transport=transport)
+        assert ctx.transport == (transport if transport != "auto" else ("mc" if ctx.mc is not None else "push"))
+        for it in range(4):
+            a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, it, dt)
+            a, b = a_all[rank].cuda(), b.cuda()
+            c = torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda")
+            ag_gemm_intra_node_op(a, b, c, ctx)
+            torch.cuda.synchronize()
+            w.check()
+            ref = torch.cat(a_all, 0).cuda().float() @ b.float().t()
+            assert (c.float() - ref).abs().max().item() < TOL, f"AG {ctx.transport} round {it}"
+        finalize_ag_gemm_context(ctx)
     # ---- GEMM + RS / AR ----------------------------------------------------
     M, N, kl = 1024, 768, 512
     rs = create_gemm_rs_intra_node_context(M, N, dt, rank, R)
@@ -71,6 +77,23 @@ def _all_ops(rank, R):
         torch.cuda.synchronize()
         w.check()
         assert (c.float() - ref).abs().max().item() < TOL, f"AR {mode} after a publish-only call"
+    # ---- GEMM + AR by recursive doubling: four panels over two staging slots --------------
+    import torch.distributed as dist
+    from tridist_b200.ops import create_gemm_ar_rd_context, finalize_gemm_ar_rd_context, gemm_ar_rd_op
+    rd = create_gemm_ar_rd_context(M, N, dt, dt, rank, R, chunk_rows=256, stage_slots=2)
+    assert rd.rd.transport == "rd" and rd.rd.num_chunks == 4
+    for it, m_now in enumerate((M, M // 2, M)):
+        a_all, b_all = ks_inputs(R, m_now, N, kl, 300 + it, dt)
+        ref = sum(a_all[s].cuda().float() @ b_all[s].cuda().float().t() for s in range(R))
+        c = torch.empty(m_now, N, dtype=dt, device="cuda")
+        gemm_ar_rd_op(a_all[rank].cuda(), b_all[rank].cuda(), c, rd)
+        torch.cuda.synchronize()
+        w.check()
+        assert (c.float() - ref).abs().max().item() < TOL, f"AR rd call {it}"
+        c0 = c.clone()
+        dist.broadcast(c0, 0)
+        assert torch.equal(c, c0), "recursive doubling must leave bit-identical results on all ranks"
+    finalize_gemm_ar_rd_context(rd)
     # ---- MoE ---------------------------------------------------------------
     E, H, topk, T = 8 * R, 1024, 4, 256
     moe = create_moe_a2a_intra_node_context(E, H, dt, T, topk, rank, R)

@@ -691,3 +691,60 @@ def test_device_side_index_check_reports_and_skips():
         w.check()
     w.clear_status()
     assert bool(torch.isfinite(out.float()).all())
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_gemm_ar_rd_emulated(R):
+    """Recursive-doubling panel exchange on virtual ranks: three panels over two staging slots (the
+    third panel reuses slot 0 under the ack ticket), several calls on one context, and an M that
+    changes between calls (tickets advance by a fixed stride per call)."""
+    from tridist_b200.ops.gemm_ar_rd import create_gemm_ar_rd_context, gemm_ar_rd_emulated
+    from tridist_b200.utils.testing import ks_inputs
+    w = _emu(R)
+    dt = torch.bfloat16
+    N, kl = 640, 192
+    ctxs = [create_gemm_ar_rd_context(384, N, dt, dt, r, R, chunk_rows=128, stage_slots=2, world=w)
+            for r in range(R)]
+    assert ctxs[0].rd.num_chunks == 3 and ctxs[0].rd.phases == R.bit_length() - 1
+    for it, M in enumerate((384, 256, 384, 128)):
+        a_all, b_all = ks_inputs(R, M, N, kl, it, dt, 0.05)
+        a_all = [x.cuda() for x in a_all]
+        b_all = [x.cuda() for x in b_all]
+        c_list = [torch.empty(M, N, dtype=dt, device="cuda") for _ in range(R)]
+        gemm_ar_rd_emulated(ctxs, a_all, b_all, c_list)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
+        for r in range(R):
+            err = (c_list[r].float() - ref).abs().max().item()
+            assert err < 3e-2, f"call {it} rank {r}: {err}"
+            assert torch.equal(c_list[r], c_list[0]), "all ranks must hold bit-identical results"
+
+
+def test_gemm_ar_rd_ack_wait_runs_out():
+    """A staging slot whose previous occupant is never acknowledged: the exchange kernel's wait
+    runs out (20 ms limit), the kernel returns with a status record naming the ack ticket, the
+    other virtual rank leaves through the abort word, and the context stays usable."""
+    from tridist_b200.ops.gemm_ar_rd import create_gemm_ar_rd_context, gemm_ar_rd_emulated
+    from tridist_b200.parallel.runtime import TriDistError
+    from tridist_b200.utils.testing import ks_inputs
+    R, M, N, kl = 2, 128, 256, 64
+    w = _emu(R)
+    w.timeout_ms = 20
+    dt = torch.float16
+    ctxs = [create_gemm_ar_rd_context(M, N, dt, dt, r, R, chunk_rows=128, stage_slots=1, world=w) for r in range(R)]
+    a_all, b_all = [[x.cuda() for x in xs] for xs in ks_inputs(R, M, N, kl, 0, dt, 0.05)]
+    c_list = [torch.empty(M, N, dtype=dt, device="cuda") for _ in range(R)]
+    ctxs[1].rd.last_ticket_per_slot[0] = 1 << 19          # an occupant nobody will ever acknowledge
+    gemm_ar_rd_emulated(ctxs, a_all, b_all, c_list)
+    torch.cuda.synchronize()
+    with pytest.raises(TriDistError, match="recursive-doubling ack ticket"):
+        w.check()
+    w.clear_status()
+    for ctx in ctxs:                                       # forget the poisoned slot; tickets only grow
+        ctx.rd.last_ticket_per_slot[0] = 0
+    gemm_ar_rd_emulated(ctxs, a_all, b_all, c_list)
+    torch.cuda.synchronize()
+    w.check()
+    ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
+    assert (c_list[0].float() - ref).abs().max().item() < 2e-2 and torch.equal(c_list[0], c_list[1])

@@ -88,14 +88,40 @@ def test_ticket_ceiling_and_ignored_argument_warnings():
     with pytest.raises(RuntimeError, match="create a new one"):
         next_round(MAX_TICKETS - 1, "reduce-scatter context")
     w = CpuWorld(0, 1)
-    with pytest.warns(UserWarning, match="stage_slots=8 has no effect"):
-        create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, stage_slots=8, world=w)
+    with pytest.warns(UserWarning, match="wait_mode='spin' has no effect"):
+        create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, wait_mode="spin", world=w)
     with warnings.catch_warnings():
         warnings.simplefilter("error")                 # defaults and honoured arguments stay silent
-        ctx = create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, chunk_rows=64, world=w)
-        assert ctx.chunk_rows == 64
+        ctx = create_gemm_ar_rd_context(256, 128, torch.float32, torch.float32, 0, 1, chunk_rows=64, stage_slots=3,
+                                        world=w)
+        assert ctx.chunk_rows == 64 and ctx.rd.stage_slots == 3 and ctx.rd.num_chunks == 4
         rs = create_gemm_rs_v5_context(256, 128, torch.float32, 0, 1, steady_sms=16, tail_chunk_window=2,
                                        chunk_rows=128, world=w)
         assert rs.reduce_ctas == 16 and rs.reduce_tail == 2
     with pytest.warns(UserWarning, match="comm_lanes=4"):
         create_gemm_rs_v5_context(256, 128, torch.float32, 0, 1, comm_lanes=4, world=w)
+
+
+def test_recursive_doubling_panels_partners_and_tickets():
+    """Host arithmetic of the panel exchange (reference rules: gemm_ar_rd.py:317-329 panel rows,
+    :424-426 XOR partners, ticket = round_base + task + 1 with a per-call stride)."""
+    import torch
+
+    from tridist_b200.ops.gemm_ar_rd import (MAX_TICKETS, _advance, create_gemm_ar_rd_context, panel_rows,
+                                             partners_of)
+    from tridist_b200.parallel.runtime import CpuWorld
+    assert partners_of(5, 8) == [4, 7, 1] and partners_of(1, 2) == [0] and partners_of(0, 1) == []
+    assert panel_rows(4096, 8192) == 512                      # 8 MB cap: 8 MB / (8192 * 2 B) = 512 rows
+    assert panel_rows(4096, 1024) == 1024                     # four panels
+    assert panel_rows(1024, 1024) == 512                      # not below min_chunk_rows
+    assert panel_rows(256, 1024) == 256                       # never above max_M
+    assert panel_rows(4096, 1024, chunk_rows=200) == 192      # caller's value, 64-row aligned
+    ctx = create_gemm_ar_rd_context(1024, 256, torch.float32, torch.float32, 0, 1, chunk_rows=256, stage_slots=2,
+                                    world=CpuWorld(0, 1))
+    rd = ctx.rd
+    assert (rd.num_chunks, rd.stage_slots, rd.round_stride, rd.phases) == (4, 2, 5, 0)
+    assert _advance(ctx, 4) == 5 and _advance(ctx, 2) == 10   # the stride does not depend on the call's M
+    rd.round_base = MAX_TICKETS - 6
+    import pytest
+    with pytest.raises(RuntimeError, match="ran out of tickets"):
+        _advance(ctx, 4)

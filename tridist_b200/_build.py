@@ -30,6 +30,7 @@ SOURCES = [
     "ops/fused_gemm.cu",
     "ops/elementwise.cu",
     "ops/moe_a2a.cu",
+    "ops/rd_exchange.cu",
     "ops/moe_local_noalloc.cu",
 ]
 

@@ -8,6 +8,7 @@
 #include "ops/elementwise.h"
 #include "ops/fused_gemm.h"
 #include "ops/moe_a2a.h"
+#include "ops/rd_exchange.h"
 #include "common/status.h"
 #include "runtime/symm_heap.h"
 #include "runtime/vmm_heap.h"
@@ -271,6 +272,47 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     wait_flag_test_launch(flag, ticket, status_dev, abort_word, timeout_ns, cur_stream(), peer_abort);
   }, py::arg("flag"), py::arg("ticket"), py::arg("status_dev"), py::arg("abort_word"), py::arg("timeout_ns"),
      py::arg("peer_abort") = std::vector<int64_t>{});
+  m.def("rd_exchange", [](std::vector<py::dict> blocks, int ctas, bool bf16) {
+    std::vector<RdRankArgs> ranks;
+    for (const auto& d : blocks) {
+      RdRankArgs a{};
+      a.c = reinterpret_cast<void*>(get<int64_t>(d, "c", 0));
+      a.ldc = get<int64_t>(d, "ldc", 0);
+      a.rows = get<int>(d, "rows", 0);
+      a.n_cols = get<int>(d, "n_cols", 0);
+      a.phases = get<int>(d, "phases", 0);
+      a.slot = get<int>(d, "slot", 0);
+      a.slots = get<int>(d, "slots", 1);
+      a.flag_slices = get<int>(d, "flag_slices", kRdMaxSlices);
+      a.slot_bytes = get<int64_t>(d, "slot_bytes", 0);
+      a.scatter = reinterpret_cast<void*>(get<int64_t>(d, "scatter", 0));
+      a.arrival = reinterpret_cast<uint32_t*>(get<int64_t>(d, "arrival", 0));
+      a.ack = reinterpret_cast<uint32_t*>(get<int64_t>(d, "ack", 0));
+      int64_t ps[3] = {0, 0, 0}, pa[3] = {0, 0, 0}, pk[3] = {0, 0, 0}, ab[8] = {0};
+      fill_ptrs(d, "peer_scatter", ps, 3);
+      fill_ptrs(d, "peer_arrival", pa, 3);
+      fill_ptrs(d, "peer_ack", pk, 3);
+      fill_ptrs(d, "peer_abort", ab, 8);
+      for (int i = 0; i < 3; ++i) {
+        a.peer_scatter[i] = reinterpret_cast<void*>(ps[i]);
+        a.peer_arrival[i] = reinterpret_cast<uint32_t*>(pa[i]);
+        a.peer_ack[i] = reinterpret_cast<uint32_t*>(pk[i]);
+      }
+      a.ticket = get<uint32_t>(d, "ticket", 0);
+      a.prev_ticket = get<uint32_t>(d, "prev_ticket", 0);
+      a.env.status = reinterpret_cast<StatusBlock*>(get<int64_t>(d, "status_dev", 0));
+      a.env.abort_word = reinterpret_cast<uint32_t*>(get<int64_t>(d, "abort_word", 0));
+      a.env.timeout_ns = get<uint64_t>(d, "timeout_ns", 4000000000ull);
+      a.env.rank = get<uint32_t>(d, "rank", 0);
+      for (int i = 0; i < 8; ++i)
+        if (ab[i]) {
+          a.env.peer_abort[i] = reinterpret_cast<uint32_t*>(ab[i]);
+          a.env.n_peers = static_cast<uint32_t>(i + 1);
+        }
+      ranks.push_back(a);
+    }
+    rd_exchange_launch(ranks, ctas, bf16, cur_stream());
+  }, py::arg("blocks"), py::arg("ctas"), py::arg("bf16"));
   m.def("fill_u32", [](int64_t p, int64_t n, uint32_t v) {
     fill_u32_launch(reinterpret_cast<uint32_t*>(p), n, v, cur_stream());
   });

@@ -23,9 +23,11 @@ enum WaitSite : uint32_t {
   SITE_MOE_META = 6,
   SITE_MOE_DISPATCH_DONE = 7,
   SITE_MOE_COMBINE_READY = 8,
-  SITE_SPLITK = 9,
-  SITE_AG_ARRIVE = 10,
-  SITE_INDEX_CHECK = 11,   // a computed ticket / row / chunk index failed its range check (nothing was accessed)     // pull all-gather: waiting for a source to stage its chunk         // split-K finisher waiting for another slice's partial
+  SITE_SPLITK = 9,         // split-K finisher waiting for another slice's partial
+  SITE_AG_ARRIVE = 10,     // pull all-gather: waiting for a source to stage its chunk
+  SITE_INDEX_CHECK = 11,   // a computed ticket / row / chunk index failed its range check (nothing was accessed)
+  SITE_RD_ARRIVAL = 12,    // recursive-doubling exchange: waiting for the partner's panel slice
+  SITE_RD_ACK = 13,        // recursive-doubling exchange: waiting for the partner to free a staging slot
   SITE_PIPE_FULL = 16,
   SITE_PIPE_EMPTY = 17,
   SITE_TMEM_FULL = 18,

@@ -193,6 +193,7 @@ struct alignas(64) GemmParams {
   uint32_t* ag_counters;           // local [R + 1][n_chunks] part counters (row R: staging of the own shard, pull)
   uint32_t* peer_ag_arrive[kMaxRanks];  // pull: [R][ag_flag_stride] "source staged its chunk" tickets on every rank
   int32_t ag_pull;                 // 1 = pull transport (stage, arrive, pull, ready), 0 = push
+  int32_t ag_mc;                   // OP_AG: the shard goes out as multimem.st through mc_part (all CTAs' comm warps)
   uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
   int32_t chunk_rows, n_chunks, push_parts;
   int32_t skip_comm;
@@ -538,6 +539,8 @@ __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __e
 // The kernel
 // ----------------------------------------------------------------------------
 template <int BN, bool kBf16, int kCtaM, bool kStaging, int kMT>
+// 320 threads are allocated as 12 warps' worth of registers: 65536 / 384 = 170, so 168 per thread
+// is all one CTA can have (a larger cap leaves no CTA resident at all).
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __restrict__ pv) {
   using TS = TileShape<BN, kCtaM, kStaging, kMT>;
@@ -590,7 +593,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     for (int i = 0; i < kPushSlots; ++i) mbar_init(&push_bar[i], 1);
     s_flags[0] = 0;
     s_flags[1] = 1;
-    s_flags[2] = pushes ? 0 : 1;
+    s_flags[2] = (pushes && !p.ag_mc) ? 0 : 1;   // (the multicast push keeps out of the operand ring)
     s_flags[3] = 0;
     mbar_fence_init();
   }
@@ -631,7 +634,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const int bands = *reinterpret_cast<volatile int32_t*>(s_tab);
 
-  const WaitEnv env = p.env;
+  // a reference into the parameter block: a local copy would be indexed dynamically
+  // (peer_abort[i]) and live on the stack, and every wait would read it from there
+  const WaitEnv& env = p.env;
   uint64_t* const prof = p.prof ? p.prof + static_cast<int64_t>(blockIdx.x) * kProfSlots : nullptr;
   const uint64_t t_kernel0 = prof ? globaltimer_ns() : 0;
 
@@ -657,7 +662,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool swiglu = p.epi == EPI_SWIGLU;
       const int up_row0 = p.swiglu_up_row0;
       const CUtensorMap* const bmap = &p.tma_b;
-      if (pushes) {
+      if (pushes && !p.ag_mc) {
         // the operand ring carries this CTA's part of the all-gather push first (the pushing
         // thread's own waits are bounded, so this one ends too; the limit is a backstop)
         const uint64_t t0 = globaltimer_ns();
@@ -768,9 +773,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
           if (!((pending >> s) & 1u)) continue;
           // the stage was armed in the most recent pass over slot s
           const uint32_t par = (s < static_cast<int>(stage)) ? phase : (phase ^ 1u);
-          WaitEnv quiet = env;
-          quiet.status = nullptr;
-          quiet.abort_word = nullptr;
+          WaitEnv quiet{};                 // no status, no abort words: this wait only drains
+          quiet.rank = env.rank;
           quiet.timeout_ns = 2000000ull;   // loads land within microseconds; never linger here
           if (leader) wait_mbar(&full_bar[s], par, quiet, SITE_PIPE_FULL, s);
         }
@@ -934,9 +938,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         // Unwinding: MMAs already issued must retire before TMEM is freed.
         if constexpr (kCtaM == 2) umma_commit_pair_local(drain_bar);
         else umma_commit(drain_bar);
-        WaitEnv quiet = env;
-        quiet.status = nullptr;
-        quiet.abort_word = nullptr;
+        WaitEnv quiet{};
+        quiet.rank = env.rank;
+        quiet.timeout_ns = env.timeout_ns;
         wait_mbar(drain_bar, 0u, quiet, SITE_TMEM_FULL, 0);
       }
     }
@@ -1396,7 +1400,48 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // its part of the push is done (its producer warp waits for s_flags[2]), which gives the
       // copy engine a dozen pieces in flight instead of two and keeps the push from competing
       // with the CTA's own operand loads.
-      if (ctid == 0) {
+      if (p.ag_mc) {
+        // ---- multicast push: one store through the switch reaches every rank's workspace, so this
+        // rank sends its shard ONCE (not once per peer) and the work is small enough for the
+        // communication warps of all CTAs to do on the side: no CTA gives up tiles for it, no
+        // shared memory is involved. Chunk-major, each CTA a slice of every chunk, so that the
+        // first rows are complete everywhere first; the last CTA to finish its slice of a chunk
+        // raises that chunk's ticket on all peers.
+        constexpr int kU = 8;                                        // 16-byte pieces in flight per thread
+        const int64_t chunk_pieces = static_cast<int64_t>(p.chunk_rows) * p.K / 8;
+        const int64_t per = (chunk_pieces + push_grid - 1) / push_grid;
+        const int64_t lo_in = min(chunk_pieces, per * static_cast<int64_t>(blockIdx.x));
+        const int64_t hi_in = min(chunk_pieces, lo_in + per);
+        const uint8_t* const src = reinterpret_cast<const uint8_t*>(p.a_local);
+        uint8_t* const dst = reinterpret_cast<uint8_t*>(p.mc_part) +
+                             static_cast<int64_t>(p.rank) * p.m_per_rank * p.K * 2;
+        for (int ck = 0; pushes && ck < p.n_chunks; ++ck) {
+          const int64_t lo = ck * chunk_pieces + lo_in, hi = ck * chunk_pieces + hi_in;
+          for (int64_t base = lo + ctid; base < hi; base += static_cast<int64_t>(kCommThreads) * kU) {
+            uint4 v[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {        // (index clamped: no branch between the loads)
+              const int64_t i = min(base + static_cast<int64_t>(u) * kCommThreads, hi - 1);
+              v[u] = ld_global_nc_v4(src + i * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const int64_t i = base + static_cast<int64_t>(u) * kCommThreads;
+              if (i < hi) multimem_st_v4(dst + i * 16, v[u]);
+            }
+          }
+          // the counter add below releases what this barrier ordered (all 128 threads' stores)
+          named_bar_sync(1, kCommThreads);
+          if (ctid == 0) {
+            uint32_t* cnt = p.ag_counters + ck;
+            if (atom_add_acq_rel_gpu(cnt, 1u) + 1u == static_cast<uint32_t>(push_grid)) {
+              atomicExch(cnt, 0u);
+              for (int d = 0; d < p.R; ++d)
+                if (d != p.rank) st_release_sys(p.peer_ag_flags[d] + p.rank * p.ag_flag_stride + ck, p.round);
+            }
+          }
+        }
+      } else if (ctid == 0) {
         constexpr uint32_t kPiece = 16384;
         constexpr int kLag = kPushSlots / 2;     // stores that may still be reading their slot
         static_assert(kPushSlots * kPiece <= TS::kStages * TS::kStageBytes, "push ring exceeds the operand ring");

@@ -428,6 +428,9 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.slot_stride = d.slot_stride;
     p.res_is_c = d.res_is_c;
     p.nvls = (d.nvls && (d.op == OP_AR2 || d.op == OP_RS) && d.R > 1) ? 1 : 0;
+    p.ag_mc = (d.nvls && d.op == OP_AG && d.R > 1 && !p.ag_pull) ? 1 : 0;
+    if (p.ag_mc && (d.mc_part[par] == 0 || d.mc_part[par] % 16 != 0 || d.K % 8 != 0))
+      throw std::runtime_error("tridist_b200: multicast all-gather needs a 16-byte aligned multicast workspace address");
     p.reduce_ctas = d.reduce_ctas;
     p.reduce_tail = d.reduce_tail;
     p.mc_part = reinterpret_cast<void*>(d.mc_part[par]);

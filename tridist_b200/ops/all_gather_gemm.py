@@ -11,12 +11,21 @@ Public API and semantics follow the reference
 * ``ag_gemm_intra_node(a, b, transe_b, ctx)`` allocates C.
 
 What differs is the mechanism: one persistent sm_100a kernel per call. Its
-communication warps push the local shard into every peer's workspace with
-16-byte stores over NVLink and raise a per-(source, chunk) ticket; its TMA warp
-waits for the ticket of a remote row block, then loads it from the local
-workspace; tcgen05 tiles run own rows first, then sources in arrival order.
-There is no host-side synchronisation and no global barrier: the workspace is
-double-buffered by call parity.
+communication warps move the local shard into every peer's workspace and raise a
+per-(source, row block) ticket; its TMA warp waits for the ticket of a remote row block,
+then loads it from the local workspace; tcgen05 tiles run own rows first, then sources in
+arrival order. There is no host-side synchronisation and no global barrier: the workspace
+is double-buffered by call parity.
+
+Transports (``transport=`` / ``TRIDIST_AG_TRANSPORT``; ``auto`` = ``mc`` where the fabric has
+multicast, else ``push``):
+
+  mc    the workspace is bound to an NVSwitch multicast object and the shard leaves as
+        ``multimem.st``: one store reaches every rank, so a rank sends its shard once instead of
+        once per peer, and the communication warps of all CTAs do it on the side
+  push  bulk copies (16 KB pieces through a shared-memory ring) into each peer's workspace by a
+        few CTAs that join the GEMM late
+  pull  every rank stages its shard in its own workspace, the consumers copy it out of the peers'
 """
 from __future__ import annotations
 
@@ -29,7 +38,7 @@ import torch
 from ..parallel import cpu_backend
 from ..parallel.runtime import (CpuWorld, EmulatedWorld, SymmBuffer, default_world, init_runtime,
                                 native)
-from ..utils.config import env_int
+from ..utils.config import env_int, env_str
 from ._gemm_common import (next_round, BM, EPI_SWIGLU, OP_AG, SCHED_NATURAL, SCHED_SEGMENT, PlanCache,
                            base_desc, choose_bn, debug_check, rotation_order, tensor_extent_bytes)
 
@@ -50,7 +59,8 @@ class AllGatherGEMMTensorParallelContext:
     ws: Optional[SymmBuffer] = None          # [2][max_M, K] gathered A, double-buffered
     flags: Optional[SymmBuffer] = None       # u32 [R, max_chunks] tickets, indexed by source
     arrive: Optional[SymmBuffer] = None      # u32 [R, max_chunks] "source staged its chunk" (pull transport)
-    transport: str = "push"                  # "push" | "pull"
+    transport: str = "push"                  # "mc" | "push" | "pull"
+    mc: Optional[object] = None              # McBuffer behind ws when the workspace is multicast-bound
     push_ctas: int = 0                       # CTAs that carry the transfer (0 = chosen from the shape)
     counters: Optional[torch.Tensor] = None  # local part counters of the transfer
     arrival_ns: Optional[torch.Tensor] = None  # int64 [R] first-seen arrival stamps (observer)
@@ -80,11 +90,11 @@ class AllGatherGEMMTensorParallelContext:
 
 def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank, num_ranks, mpi=None,
                                       comm=None, M_PER_CHUNK=1024, ag_stream=None, gemm_stream=None,
-                                      world=None):
+                                      world=None, transport: Optional[str] = None):
     """Collective. Allocates the symmetric workspace and ticket planes.
 
     ``mpi`` is accepted for signature compatibility and ignored; ``comm`` may be
-    a ``torch.distributed`` process group.
+    a ``torch.distributed`` process group. ``transport``: see the module docstring.
     """
     assert max_M % num_ranks == 0, "max_M must be divisible by num_ranks"
     m_pr = max_M // num_ranks
@@ -100,13 +110,69 @@ def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
     if isinstance(world, CpuWorld):
         return ctx
     assert input_dtype == output_dtype, "the fused kernel emits the input dtype"
-    ctx.ws = world.alloc(2 * max_M * K * 2, rank)
+    want = transport or env_str("TRIDIST_AG_TRANSPORT", "auto")
+    assert want in ("auto", "mc", "push", "pull")
+    ws_bytes = 2 * max_M * K * 2
+    if num_ranks > 1 and want in ("auto", "mc") and env_int("TRIDIST_NVLS", 1):
+        ctx.mc = world.alloc_multicast(ws_bytes)
+    if want == "mc" and ctx.mc is None:
+        raise RuntimeError("tridist_b200: transport 'mc' needs a multicast-bound workspace: "
+                           + str(getattr(world, "multicast_unavailable", "not a multi-process world")))
+    ctx.ws = ctx.mc if ctx.mc is not None else world.alloc(ws_bytes, rank)
+    ctx.transport = "mc" if ctx.mc is not None else ("pull" if want == "pull" else "push")
     ctx.flags = world.alloc(num_ranks * ctx.max_chunks * 4, rank)
     ctx.arrive = world.alloc(num_ranks * ctx.max_chunks * 4, rank)
     ctx.counters = torch.zeros((num_ranks + 1) * ctx.max_chunks, dtype=torch.int32, device="cuda")
     ctx.arrival_ns = torch.zeros(num_ranks, dtype=torch.int64, device="cuda")
+    if ctx.mc is not None and env_int("TRIDIST_NVLS_SELFTEST", 1):
+        _mc_selftest(ctx)
     world.host_barrier()
     return ctx
+
+
+def _mc_selftest(ctx) -> None:
+    """Collective. Two small all-gathers of known integers through the multicast workspace (both
+    parities); if any rank sees a wrong value or a kernel-reported failure, all ranks drop the
+    multicast workspace together and the context falls back to the bulk-copy push."""
+    import torch.distributed as dist
+    world, R, rank = ctx.world, ctx.num_ranks, ctx.rank
+    m_pr = min(ctx.max_M // R, 128)
+    dev = torch.device("cuda", world.device)
+    a = torch.full((m_pr, ctx.K), float(rank + 1), dtype=ctx.input_dtype, device=dev)
+    b = torch.zeros((128, ctx.K), dtype=ctx.input_dtype, device=dev)
+    b[:, :64] = 1.0
+    why = ""
+    try:
+        for _ in range(2):
+            c = torch.empty((m_pr * R, 128), dtype=ctx.output_dtype, device=dev)
+            ag_gemm_intra_node_op(a, b, c, ctx)
+            torch.cuda.synchronize()
+            world.check()
+            expect = (torch.arange(R, device=dev).repeat_interleave(m_pr).float() + 1.0) * 64.0
+            bad = int((c.float() != expect[:, None]).sum().item())
+            if bad:
+                why = f"{bad} of {c.numel()} values differ"
+                break
+    except Exception as exc:
+        why = f"{type(exc).__name__}: {exc}"
+        try:
+            world.clear_status()
+        except Exception:
+            pass
+    ctx.plans.clear()
+    verdicts = [None] * R
+    dist.all_gather_object(verdicts, why, group=world.group)
+    if any(verdicts):
+        world.multicast_unavailable = "all-gather self-test failed: " + "; ".join(
+            f"rank {r}: {v}" for r, v in enumerate(verdicts) if v)
+        world.free_multicast(ctx.mc)
+        ctx.mc = None
+        ctx.ws = world.alloc(2 * ctx.max_M * ctx.K * 2, rank)
+        ctx.transport = "push"
+        ctx.flag_round = 0
+        for buf in (ctx.flags, ctx.arrive):
+            native().fill_u32(buf.local_ptr, buf.nbytes // 4, 0)
+        torch.cuda.synchronize()
 
 
 def _ticket_rows(ctx, m_pr: int) -> int:
@@ -209,8 +275,14 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["push_parts"] = _push_parts(chunk, K)
             # A subset of the CTAs carries the push (their operand ring is the copy ring
             # meanwhile) and joins the GEMM as many rounds late as the push takes.
-            d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn,
-                                                               ctx.push_ctas)
+            if ctx.transport == "mc":
+                # every CTA's communication warps send a slice; nobody sits out a round
+                d["nvls"] = 1
+                d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + half]
+                d["push_ctas"], d["push_skip_rounds"] = 0, 0
+            else:
+                d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn,
+                                                                   ctx.push_ctas)
             if ctx.transport == "pull":
                 d["ag_pull"] = 1
                 d["peer_ag_arrive"] = ctx.arrive.ptrs()
@@ -296,7 +368,11 @@ def finalize_ag_gemm_context(ctx) -> None:
         return
     ctx.plans.clear()
     if not isinstance(ctx.world, EmulatedWorld):
-        ctx.world.free(ctx.ws)
+        if ctx.mc is not None:
+            ctx.world.free_multicast(ctx.mc)
+            ctx.mc = None
+        else:
+            ctx.world.free(ctx.ws)
         ctx.world.free(ctx.flags)
         if ctx.arrive is not None:
             ctx.world.free(ctx.arrive)

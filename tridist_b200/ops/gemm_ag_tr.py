@@ -41,10 +41,11 @@ def create_gemm_ag_tr_context(max_M, K, input_dtype, output_dtype, rank, num_ran
     if m_pr % 128 != 0:
         rows = m_pr
     ctx = create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank, num_ranks, mpi, comm,
-                                            M_PER_CHUNK=rows, world=world)
+                                            M_PER_CHUNK=rows, world=world, transport=transport)
     ctx.chunk_rows = rows
-    assert transport in ("pull", "push")
-    ctx.transport = transport
+    assert transport in ("pull", "push", "mc", "auto")
+    if transport in ("pull", "push"):
+        ctx.transport = transport
     if comm_lanes != 2:
         ctx.push_ctas = max(2, 8 * int(comm_lanes))
     warn_ignored("create_gemm_ag_tr_context", wait_mode=(wait_mode, None))

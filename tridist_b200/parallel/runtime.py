@@ -38,7 +38,8 @@ class TriDistError(RuntimeError):
 SITE_NAMES = {
     1: "all-gather chunk ticket", 2: "reduce-scatter tile ticket", 3: "all-reduce tile ticket",
     4: "all-reduce result ticket", 5: "barrier", 6: "MoE metadata", 7: "MoE dispatch completion",
-    8: "MoE combine readiness", 9: "split-K partial", 10: "all-gather arrive ticket", 11: "index range check", 16: "pipeline full barrier", 17: "pipeline empty barrier",
+    8: "MoE combine readiness", 9: "split-K partial", 10: "all-gather arrive ticket", 11: "index range check",
+    12: "recursive-doubling arrival ticket", 13: "recursive-doubling ack ticket", 16: "pipeline full barrier", 17: "pipeline empty barrier",
     18: "TMEM full barrier", 19: "TMEM empty barrier", 32: "self test",
 }
 CODE_NAMES = {1: "flag wait timed out", 2: "pipeline barrier wait timed out",

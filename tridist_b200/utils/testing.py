@@ -81,23 +81,27 @@ def spawn(fn: Callable, world_size: int, backend: str = "gloo", args: tuple = ()
 # ---------------------------------------------------------------------------
 # Seeded inputs
 # ---------------------------------------------------------------------------
-def randn_seeded(shape, seed: int, scale: float = 1.0, dtype=torch.float32) -> torch.Tensor:
-    g = torch.Generator(device="cpu")
+def randn_seeded(shape, seed: int, scale: float = 1.0, dtype=torch.float32, device="cpu") -> torch.Tensor:
+    """Seeded normal data. The same (seed, device kind) gives the same values in every process,
+    which is what lets each rank rebuild the other ranks' operands for its reference result;
+    ``device="cuda"`` generates on the GPU (a long soak would otherwise be bound by the host's
+    random-number generation)."""
+    g = torch.Generator(device=device)
     g.manual_seed(seed)
-    return (torch.randn(shape, generator=g, dtype=torch.float32) * scale).to(dtype)
+    return (torch.randn(shape, generator=g, dtype=torch.float32, device=device) * scale).to(dtype)
 
 
-def ag_inputs(rank: int, R: int, m_pr: int, K: int, n_pr: int, it: int, dtype, scale=0.02):
+def ag_inputs(rank: int, R: int, m_pr: int, K: int, n_pr: int, it: int, dtype, scale=0.02, device="cpu"):
     """Per-rank A shards (seed by source rank and iteration) and this rank's B."""
-    a_all = [randn_seeded((m_pr, K), 1000 + 17 * it + s, scale, dtype) for s in range(R)]
-    b = randn_seeded((n_pr, K), 5000 + 31 * it + rank, scale, dtype)
+    a_all = [randn_seeded((m_pr, K), 1000 + 17 * it + s, scale, dtype, device) for s in range(R)]
+    b = randn_seeded((n_pr, K), 5000 + 31 * it + rank, scale, dtype, device)
     return a_all, b
 
 
-def ks_inputs(R: int, M: int, N: int, k_loc: int, it: int, dtype, scale=0.02):
+def ks_inputs(R: int, M: int, N: int, k_loc: int, it: int, dtype, scale=0.02, device="cpu"):
     """K-sharded operands of every rank (GEMM+RS / GEMM+AR): each source pairs its own B."""
-    a_all = [randn_seeded((M, k_loc), 2000 + 13 * it + s, scale, dtype) for s in range(R)]
-    b_all = [randn_seeded((N, k_loc), 7000 + 29 * it + s, scale, dtype) for s in range(R)]
+    a_all = [randn_seeded((M, k_loc), 2000 + 13 * it + s, scale, dtype, device) for s in range(R)]
+    b_all = [randn_seeded((N, k_loc), 7000 + 29 * it + s, scale, dtype, device) for s in range(R)]
     return a_all, b_all
 
 
