@@ -77,6 +77,7 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   g.allow_wide = get<int>(d, "allow_wide", 1);
   g.allow_splitk = get<int>(d, "allow_splitk", 1);
   g.raster_g = get<int>(d, "raster_g", 0);
+  g.l2_ahead = get<int>(d, "l2_ahead", 0);
   fill_ptrs2(d, "peer_ws", g.peer_ws);
   fill_ptrs(d, "peer_ag_flags", g.peer_ag_flags, 8);
   fill_ptrs(d, "peer_ag_arrive", g.peer_ag_arrive, 8);
@@ -313,6 +314,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     rd_exchange_launch(ranks, ctas, bf16, cur_stream());
   }, py::arg("blocks"), py::arg("ctas"), py::arg("bf16"));
+  m.def("stamp_globaltimer", [](int64_t out) { stamp_globaltimer_launch(out, cur_stream()); });
   m.def("fill_u32", [](int64_t p, int64_t n, uint32_t v) {
     fill_u32_launch(reinterpret_cast<uint32_t*>(p), n, v, cur_stream());
   });

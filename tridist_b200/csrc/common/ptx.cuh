@@ -212,16 +212,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* m,
-                                                 uint64_t* bar, int32_t x, int32_t y,
-                                                 uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;"
-      :
-      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x),
-        "r"(y), "l"(policy)
-      : "memory");
+// Asks L2 for one box of a tiled tensor ahead of the load that will need it (no shared memory,
+// no completion to wait for). Same alignment rule for x as the load.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
+               : "memory");
 }
 
 // 2-D tiled store shared -> global (bulk async-group completion).

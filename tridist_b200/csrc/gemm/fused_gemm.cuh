@@ -136,6 +136,9 @@ enum ProfSlot : int {
   PROF_TL_COMM_START = 25,   // communication warps: entry
   PROF_TL_OWN_IT0 = 26,      // owner: first batch of the reduce loop stored (cold-start cost)
   PROF_SK_WAIT = 27,         // epilogue: split-K finisher waiting for the other slices' partials
+  PROF_T_ENTRY = 28,         // absolute globaltimer: first instruction of the CTA
+  PROF_T_SETUP = 29,         // absolute globaltimer: barriers initialised, TMEM allocated, roles start
+  PROF_T_END = 30,           // absolute globaltimer: CTA done
   kProfSlots = 32,
 };
 
@@ -194,6 +197,7 @@ struct alignas(64) GemmParams {
   uint32_t* peer_ag_arrive[kMaxRanks];  // pull: [R][ag_flag_stride] "source staged its chunk" tickets on every rank
   int32_t ag_pull;                 // 1 = pull transport (stage, arrive, pull, ready), 0 = push
   int32_t ag_mc;                   // OP_AG: the shard goes out as multimem.st through mc_part (all CTAs' comm warps)
+  int32_t l2_ahead;                // k-blocks the producer asks L2 for ahead of its loads (0 = none)
   uint64_t* arrival_ns;            // optional [R] first-observed arrival stamps (skew observer)
   int32_t chunk_rows, n_chunks, push_parts;
   int32_t skip_comm;
@@ -549,6 +553,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
   // indexes the rank and each rank reads its own parameter block.
   const GemmParams& p = pv ? pv[blockIdx.y] : p0;
 
+  const uint64_t t_entry = p.prof ? globaltimer_ns() : 0;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;
   uint8_t* staging = smem + TS::kStages * TS::kStageBytes;
@@ -662,6 +667,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const bool swiglu = p.epi == EPI_SWIGLU;
       const int up_row0 = p.swiglu_up_row0;
       const CUtensorMap* const bmap = &p.tma_b;
+      const int ahead = p.l2_ahead;
       if (pushes && !p.ag_mc) {
         // the operand ring carries this CTA's part of the all-gather push first (the pushing
         // thread's own waits are bounded, so this one ends too; the limit is a backstop)
@@ -721,11 +727,26 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
         const int b_row_pair = swiglu
             ? (sub == 0 ? t.n_tile * (BN / 2) : up_row0 + t.n_tile * (BN / 2))
             : n0 + sub * (BN / 2);
+        // L2 look-ahead: the ring holds about a microsecond of operands, less than a DRAM access
+        // under load, so a tile whose operands are not in L2 yet (a cold start, a new column
+        // block of B) would run at DRAM latency. The box `ahead` k-blocks on is requested now;
+        // at the start of a tile the first `ahead` boxes are requested in one go.
+        const int b_row_pf = (kCtaM == 2) ? b_row_pair : (swiglu ? t.n_tile * (BN / 2) : n0);
+        const int b_row_pf2 = swiglu ? up_row0 + t.n_tile * (BN / 2) : n0 + 128;
+        auto l2_request = [&](int kb) {
+#pragma unroll
+          for (int h = 0; h < kMT; ++h) tma_prefetch_l2_2d(amap, kb * BK, a_row + h * BM);
+          tma_prefetch_l2_2d(bmap, kb * BK, b_row_pf);
+          if (kCtaM == 1 && BN == 256) tma_prefetch_l2_2d(bmap, kb * BK, b_row_pf2);
+        };
+        if (ahead > 0 && probe == 0)
+          for (int kb = wi.kb0 + 1; kb < wi.kb1 && kb < wi.kb0 + ahead; ++kb) l2_request(kb);
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (probe == 1) {
             if (loads_issued >= TS::kStages) break;   // ring filled once, then idle
             ++loads_issued;
           }
+          if (ahead > 0 && kb + ahead < wi.kb1 && probe == 0) l2_request(kb + ahead);
           if (prof && !mbar_try_wait(&empty_bar[stage], phase ^ 1u)) {
             const uint64_t tw = globaltimer_ns();
             ok = wait_mbar(&empty_bar[stage], phase ^ 1u, env, SITE_PIPE_EMPTY, stage);
@@ -1847,7 +1868,13 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     if constexpr (kCtaM == 2) tmem_dealloc_pair(tmem_base, TS::kTmemCols);
     else tmem_dealloc(tmem_base, TS::kTmemCols);
   }
-  if (prof && threadIdx.x == 0) prof[PROF_KERNEL] = globaltimer_ns() - t_kernel0;
+  if (prof && threadIdx.x == 0) {
+    const uint64_t t_end = globaltimer_ns();
+    prof[PROF_KERNEL] = t_end - t_kernel0;
+    prof[PROF_T_ENTRY] = t_entry;
+    prof[PROF_T_SETUP] = t_kernel0;
+    prof[PROF_T_END] = t_end;
+  }
 }
 
 }  // namespace tdb

@@ -162,6 +162,15 @@ void wait_flag_test_launch(int64_t flag, uint32_t ticket, int64_t status_dev, in
   launch_count_add(1);
 }
 
+// One thread writes the global timer: a time stamp in stream order, on the clock the kernels'
+// own accounting uses (so that "when did the previous kernel end" can be placed on a CTA time line).
+__global__ void stamp_kernel(uint64_t* out) { *out = globaltimer_ns(); }
+
+void stamp_globaltimer_launch(int64_t out, void* stream_) {
+  stamp_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(reinterpret_cast<uint64_t*>(out));
+  check(cudaGetLastError(), "stamp launch");
+}
+
 __global__ void fill_u32_kernel(uint32_t* p, int64_t n, uint32_t v) {
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x)

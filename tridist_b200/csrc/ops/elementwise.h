@@ -29,6 +29,9 @@ void wait_flag_test_launch(int64_t flag, uint32_t ticket, int64_t status_dev, in
 
 void fill_u32_launch(uint32_t* p, int64_t n, uint32_t v, void* stream);
 
+// Writes the device's global timer (ns) to `out` (8 bytes of device memory) in stream order.
+void stamp_globaltimer_launch(int64_t out, void* stream);
+
 // Recomputes `spots` pseudo-randomly chosen elements of every 128 x bn tile of
 // C = A @ B^T in fp32 and sets bad_tiles[tile] = 1 where |c - ref| > tol * (1 + |ref|).
 void spot_verify_launch(int64_t a, int64_t b, int64_t c, int M, int N, int K, int64_t lda,

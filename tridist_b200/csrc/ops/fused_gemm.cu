@@ -429,6 +429,7 @@ int64_t gemm_plan_create(const GemmPlanDesc& d) {
     p.res_is_c = d.res_is_c;
     p.nvls = (d.nvls && (d.op == OP_AR2 || d.op == OP_RS) && d.R > 1) ? 1 : 0;
     p.ag_mc = (d.nvls && d.op == OP_AG && d.R > 1 && !p.ag_pull) ? 1 : 0;
+    p.l2_ahead = d.l2_ahead < 0 ? 0 : (d.l2_ahead > 32 ? 32 : d.l2_ahead);
     if (p.ag_mc && (d.mc_part[par] == 0 || d.mc_part[par] % 16 != 0 || d.K % 8 != 0))
       throw std::runtime_error("tridist_b200: multicast all-gather needs a 16-byte aligned multicast workspace address");
     p.reduce_ctas = d.reduce_ctas;

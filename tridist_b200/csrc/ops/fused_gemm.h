@@ -43,6 +43,7 @@ struct GemmPlanDesc {
   int allow_wide = 1;   // let CTA pairs take 512 x 256 tiles (256 rows per CTA) where the rows allow
   int allow_splitk = 1; // let the tiles of the last, partial scheduling round be cut along K
   int raster_g = 0;     // row units walked together (0 = sized so that their A rows stay in L2)
+  int l2_ahead = 0;      // k-blocks of L2 look-ahead of the operand loads (0 = none)
   // all-gather
   int64_t peer_ws[2][8] = {};
   int64_t peer_ag_flags[8] = {};

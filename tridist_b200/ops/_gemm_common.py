@@ -117,7 +117,9 @@ PROF_SLOTS = ["load_flag_wait", "load_empty_wait", "mma_full_wait", "mma_tmem_wa
               "ar_collect_wait", "ar_collect_copy", "epi_done_at", "ar_owner_done_at",
               # time stamps (since the CTA started) of the last tile each role handled
               "tl_acc_ready", "tl_staged", "tl_stored", "tl_flagged", "tl_own_seen", "tl_own_loaded",
-              "tl_own_fenced", "tl_own_flagged", "tl_col_seen", "tl_comm_start", "tl_own_it0", "sk_wait"]
+              "tl_own_fenced", "tl_own_flagged", "tl_col_seen", "tl_comm_start", "tl_own_it0", "sk_wait",
+              # absolute globaltimer values (ns): CTA entry, roles start, CTA end
+              "t_entry", "t_setup", "t_end"]
 PROF_WIDTH = 32
 _prof_buf: Optional[torch.Tensor] = None
 
@@ -171,6 +173,7 @@ def base_desc(world, rank: int, R: int, a: torch.Tensor, b: torch.Tensor, c_ptr:
              poll_ns=env_int("TRIDIST_POLL_NS", 0),
              allow_wide=env_int("TRIDIST_WIDE", 1), allow_splitk=env_int("TRIDIST_SPLITK", 1),
              raster_g=env_int("TRIDIST_RASTER_G", 0),
+             l2_ahead=env_int("TRIDIST_L2_AHEAD", 0),
              prof=(prof_buffer().data_ptr() if prof_buffer() is not None else 0),
              # several virtual ranks in one launch keep to single-CTA tiles unless TRIDIST_EMU_PAIR=1
              # asks for CTA pairs there too (a cooperative launch of clusters)

@@ -12,10 +12,15 @@ TRIDIST_CTA_PAIR          0: never run 256-wide tiles on CTA pairs (2-CTA tcgen0
 TRIDIST_WIDE              0: never use the 512 x 256 pair tile (two 128-row blocks per CTA); default 1
 TRIDIST_SPLITK            0: never cut the tiles of the last, partial round along K; default 1
 TRIDIST_RASTER_G          row units per raster group (default: as many as keep a group's A slab within 48 MB)
+TRIDIST_L2_AHEAD          k-blocks of L2 look-ahead the operand loads request (default 0 = none: measured slower on every shape tried)
 TRIDIST_PUSH_CTAS         CTAs that drive the all-gather push (default: from the shard size and the time the
                           GEMM takes, 34 GB/s per CTA up to the link's 560 GB/s; 0 = all)
 TRIDIST_PUSH_SKIP         scheduling rounds the pushing CTAs sit out (default: what their push costs them)
 TRIDIST_AG_TICKET_ROWS    rows of a gathered shard covered by one arrival ticket (default 256)
+TRIDIST_AG_TRANSPORT      "auto" | "mc" | "push" | "pull": how the all-gather shard travels (auto = multicast
+                          stores through the switch where the fabric has them, else the bulk-copy push)
+TRIDIST_RD_TRANSPORT      "rd" (default: panel exchange with XOR partners) | "mesh" (the fused all-reduce kernel)
+                          for the gemm_ar_rd entry points; TRIDIST_RD_CTAS = CTAs of the exchange kernel (16)
 TRIDIST_RS_MODE           "auto" | "slots" | "nvls": reduce-scatter through peer-written slots or through the
                           switch (multimem.ld_reduce by the owner); auto = nvls wherever a multicast buffer exists
 TRIDIST_DEBUG             1: before a plan is created, replay its tile schedule on the host and check every
