@@ -154,3 +154,31 @@ def test_reduce_scatter_through_the_switch_walks_owners_in_lockstep(R):
     by_pos = sorted({(t[4], t[0] // rows_per_seg) for cta in dumps[0] for t in cta})
     owners = [o for _, o in by_pos]
     assert owners[:2 * R] == list(range(R)) * 2
+
+
+def test_own_first_band_major_walk():
+    """The walk of the multicast all-gather: the rank's own segment whole, then row unit b of every
+    other source (in the order's sequence) before row unit b + 1 of any. Every tile exactly once."""
+    R, rank, M, N = 8, 2, 8192, 6144
+    order = rotation_order(rank, R, 1, own_last=False)
+    out = _dump(op=OP_AG, sched=SCHED_SEGMENT, R=R, rank=rank, M=M, N=N, K=12288, m_per_rank=M // R,
+                seg_order=order, seg_bands=-1, seg_own_first=1, allow_splitk=0)
+    seen = [(t[0], t[1]) for cta in out for t in cta]
+    assert len(seen) == len(set(seen)) and set(seen) == _tiles(M, N, 256)
+    # positions are dealt round-robin: item i of worker w is position i * workers + w; a worker is a
+    # CTA pair whose two CTAs hold two row blocks each (512-row units)
+    workers = len(out) // 2
+    by_pos = {}
+    for w in range(workers):
+        for i, t in enumerate(out[2 * w][0::2]):
+            by_pos[i * workers + w] = t[0] // 4          # row unit of the position
+    units = [by_pos[k] for k in sorted(by_pos)]
+    seg_units = (M // R) // 512
+    n_tiles = N // 256
+    src_of = [u // seg_units for u in units]
+    band_of = [u % seg_units for u in units]
+    own = seg_units * n_tiles
+    assert set(src_of[:own]) == {rank}
+    rest = list(zip(band_of[own:], src_of[own:]))
+    assert rest == sorted(rest, key=lambda bs: (bs[0], order.index(bs[1]))), "band-major over the other sources"
+    assert rank not in src_of[own:]

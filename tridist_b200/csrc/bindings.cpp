@@ -68,6 +68,7 @@ static GemmPlanDesc gemm_desc_from(const py::dict& d) {
   g.strided_interleave = get<int>(d, "strided_interleave", 0);
   g.seg_interleave = get<int>(d, "seg_interleave", 0);
   g.seg_bands = get<int>(d, "seg_bands", 0);
+  g.seg_own_first = get<int>(d, "seg_own_first", 0);
   fill_ptrs(d, "peer_abort", g.peer_abort, 8);
   g.tile_list = get<int64_t>(d, "tile_list", 0);
   g.list_len = get<int>(d, "list_len", 0);

@@ -170,6 +170,7 @@ struct alignas(64) GemmParams {
   // it and R spin budgets behind it, and the kernel honours all of them (see the kernel prologue)
   int32_t table_has_header;
   int32_t seg_bands;           // SCHED_SEGMENT: row bands per segment walked band-major (1 = source-major)
+  int32_t seg_own_first;       // band-major walk: the whole first segment of the order (own rows) before the bands of the others
   const int32_t* tile_list;    // SCHED_LIST: row-major tile ids
   int32_t list_len;
   int32_t m_per_rank;      // rows per rank (AG source shard / RS owner block)
@@ -278,12 +279,31 @@ __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const
   if (p.sched == SCHED_SEGMENT && bands > 1 && !p.seg_interleave && p.seg_m_tiles % bands == 0) {
     const int band_units = p.seg_m_tiles / bands;
     const int per_band = band_units * p.n_tiles;
-    const int b = pos / (p.R * per_band);
-    const int rem = pos - b * (p.R * per_band);
-    const int si = rem / per_band;
-    const int u = rem - si * per_band;
-    raster_grouped(u, band_units, p.n_tiles, p.raster_g, um, nt);
-    um += order[si] * p.seg_m_tiles + b * band_units;
+    const int per_seg = p.seg_m_tiles * p.n_tiles;
+    if (p.seg_own_first && p.R > 1) {
+      // the first segment of the order (this rank's own rows, which need no transfer) whole, then
+      // band b of every other source before band b + 1 of any: the order in which a transfer
+      // that sends every source's rows at the same rate (multicast) completes them
+      if (pos < per_seg) {
+        raster_grouped(pos, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
+        um += order[0] * p.seg_m_tiles;
+      } else {
+        const int q = pos - per_seg;
+        const int b = q / ((p.R - 1) * per_band);
+        const int rem = q - b * ((p.R - 1) * per_band);
+        const int si = 1 + rem / per_band;
+        const int u = rem - (si - 1) * per_band;
+        raster_grouped(u, band_units, p.n_tiles, p.raster_g, um, nt);
+        um += order[si] * p.seg_m_tiles + b * band_units;
+      }
+    } else {
+      const int b = pos / (p.R * per_band);
+      const int rem = pos - b * (p.R * per_band);
+      const int si = rem / per_band;
+      const int u = rem - si * per_band;
+      raster_grouped(u, band_units, p.n_tiles, p.raster_g, um, nt);
+      um += order[si] * p.seg_m_tiles + b * band_units;
+    }
   } else if (p.sched == SCHED_SEGMENT) {
     const int per_seg = p.seg_m_tiles * p.n_tiles;
     // interleaved: every rank walks the segments in lockstep (tile k of every owner, then tile

@@ -156,6 +156,9 @@ static void fill_schedule_fields(const GemmPlanDesc& d, int cta_m, int cta_mt, G
   p.strided_interleave = d.strided_interleave;
   p.seg_interleave = (d.sched == SCHED_SEGMENT) ? d.seg_interleave : 0;
   p.seg_bands = (d.sched == SCHED_SEGMENT && d.seg_bands > 1) ? d.seg_bands : 1;
+  // seg_bands < 0: as many bands as a segment has row units (one unit per band)
+  if (d.sched == SCHED_SEGMENT && d.seg_bands < 0 && p.seg_m_tiles > 1) p.seg_bands = p.seg_m_tiles;
+  p.seg_own_first = (d.seg_own_first && p.seg_bands > 1) ? 1 : 0;
   p.list_len = d.list_len;
   p.swiglu_up_row0 = d.swiglu_up_row0;
   p.chunk_rows = d.chunk_rows > 0 ? d.chunk_rows : p.m_per_rank;

@@ -34,6 +34,7 @@ struct GemmPlanDesc {
   int check_residency = 0;      // refuse a plan whose grid cannot be resident in one wave (needs a device)
   int strided_interleave = 0;
   int seg_bands = 0;        // SCHED_SEGMENT: row bands per segment walked band-major (0 / 1 = source-major)
+  int seg_own_first = 0; // band-major walk: the order's first segment whole, then the bands of the others
   int seg_interleave = 0;   // SCHED_SEGMENT: all ranks walk the segments in lockstep (tile k of every segment, then k + 1)
   int64_t tile_list = 0;
   int list_len = 0;

@@ -280,6 +280,10 @@ def _plan(ctx, a, b, c, swiglu=False):
                 d["nvls"] = 1
                 d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + half]
                 d["push_ctas"], d["push_skip_rounds"] = 0, 0
+                if not d["seg_bands"] and baked_table is None and ctx.order_override is None:
+                    # every source's rows arrive at the same rate: own rows first, then the first
+                    # row unit of every source, then the second ...
+                    d["seg_bands"], d["seg_own_first"] = -1, 1
             else:
                 d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn,
                                                                    ctx.push_ctas)

@@ -179,7 +179,7 @@ def _plan(ctx, a, b, c, mode, parity):
     R, rank = ctx.num_ranks, ctx.rank
     M, K = a.shape
     N = b.shape[0]
-    bn = choose_bn(M, N, K=K)
+    bn = choose_bn(M, N, K=K if ctx.num_ranks == 1 else 0)   # (wide tiles halve the CTAs that publish and reduce)
     res_is_c = 0
     plane = ctx.max_M * ctx.N * 2
     if mode in ("two_shot", "nvls"):
