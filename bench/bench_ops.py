@@ -188,6 +188,16 @@ def main():
                 pr = prof_of(lambda: gemm_ar_intra_node_op(a, b, ctx.symm_output(M) if R > 1 else c, ctx))
                 if pr:
                     cell["prof_us_" + mode] = pr
+            if R > 1 and R & (R - 1) == 0 and M >= 256:
+                # the recursive-doubling transport of the "rd" entry points: panel GEMMs + XOR-partner exchange
+                from tridist_b200.ops import (create_gemm_ar_rd_context, finalize_gemm_ar_rd_context,
+                                              gemm_ar_rd_op)
+                rd = create_gemm_ar_rd_context(M, N, dt, dt, rank, R, transport="rd")
+                gemm_ar_rd_op(a, b, c, rd)
+                cell["err_rd"] = (c.float() - ref).abs().max().item()
+                cell["fused_rd"] = t(lambda: gemm_ar_rd_op(a, b, c, rd))
+                cell["rd_panels"] = -(-M // rd.rd.chunk_rows)
+                finalize_gemm_ar_rd_context(rd)
             cell["fused_gemm_only"] = t(lambda: gemm_ar_intra_node_op(a, b, c, ctx, component="gemm"))
             cell["cublas_nccl"] = t(lambda: base(a, b))
             cell["cublas_only"] = t(lambda: torch.matmul(a, b.t(), out=base.c))

@@ -125,3 +125,45 @@ def test_recursive_doubling_panels_partners_and_tickets():
     import pytest
     with pytest.raises(RuntimeError, match="ran out of tickets"):
         _advance(ctx, 4)
+
+
+def test_plan_cache_is_lru_and_reports_thrashing(monkeypatch):
+    """Plans are keyed by operand addresses: stable buffers hit, fresh addresses every call evict and
+    (after a while) warn."""
+    import warnings
+
+    import pytest
+
+    from tridist_b200.ops import _gemm_common as gc
+
+    destroyed = []
+
+    class FakeNative:
+        @staticmethod
+        def gemm_plan_destroy(pid):
+            destroyed.append(pid)
+
+    monkeypatch.setattr(gc, "native", lambda: FakeNative)
+    made = []
+
+    def maker(k):
+        def make():
+            made.append(k)
+            return 100 + len(made)
+        return make
+
+    c = gc.PlanCache(capacity=2)
+    a = c.get(("a",), maker("a"))
+    b = c.get(("b",), maker("b"))
+    assert c.get(("a",), maker("a")) == a and made == ["a", "b"] and (c.hits, c.misses) == (1, 2)
+    c.get(("c",), maker("c"))                      # evicts b, the least recently used
+    assert destroyed == [b] and c.evictions == 1
+    assert c.get(("a",), maker("a")) == a          # still cached
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        for i in range(6):                         # 1 + 6 evictions < 4 * capacity: silent
+            c.get(("x", i), maker(i))
+    with pytest.warns(UserWarning, match="reuse buffers"):
+        c.get(("x", 99), maker(99))
+    c.clear()
+    assert len(destroyed) == 1 + 7 + 2

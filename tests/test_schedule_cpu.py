@@ -179,6 +179,11 @@ def test_own_first_band_major_walk():
     band_of = [u % seg_units for u in units]
     own = seg_units * n_tiles
     assert set(src_of[:own]) == {rank}
-    rest = list(zip(band_of[own:], src_of[own:]))
-    assert rest == sorted(rest, key=lambda bs: (bs[0], order.index(bs[1]))), "band-major over the other sources"
+    bands = band_of[own:]
+    assert bands == sorted(bands), "band b of every other source before band b + 1 of any"
     assert rank not in src_of[own:]
+    # inside a band the area of all other sources is walked in groups, column by column: the
+    # tiles of one round of 74 workers share a handful of B column blocks
+    first_round = [t for w in range(workers) for t in out[2 * w][0:2]][0::2]
+    later = [by_pos[k] for k in sorted(by_pos) if own <= k < own + workers]
+    assert len(set(later)) >= 3, "several sources side by side"

@@ -282,19 +282,23 @@ __host__ __device__ __forceinline__ TileCoord tile_at(const GemmParams& p, const
     const int per_seg = p.seg_m_tiles * p.n_tiles;
     if (p.seg_own_first && p.R > 1) {
       // the first segment of the order (this rank's own rows, which need no transfer) whole, then
-      // band b of every other source before band b + 1 of any: the order in which a transfer
+      // band b of all other sources before band b + 1 of any: the order in which a transfer
       // that sends every source's rows at the same rate (multicast) completes them
       if (pos < per_seg) {
         raster_grouped(pos, p.seg_m_tiles, p.n_tiles, p.raster_g, um, nt);
         um += order[0] * p.seg_m_tiles;
       } else {
+        // band b of all other sources is ONE raster area of (R - 1) * band_units row units, walked
+        // in groups column by column like any other area: concurrent tiles share their B column
+        // blocks (a walk source by source inside the band would stream all of B once per row unit)
         const int q = pos - per_seg;
-        const int b = q / ((p.R - 1) * per_band);
-        const int rem = q - b * ((p.R - 1) * per_band);
-        const int si = 1 + rem / per_band;
-        const int u = rem - (si - 1) * per_band;
-        raster_grouped(u, band_units, p.n_tiles, p.raster_g, um, nt);
-        um += order[si] * p.seg_m_tiles + b * band_units;
+        const int area_units = (p.R - 1) * band_units;
+        const int b = q / (area_units * p.n_tiles);
+        const int u = q - b * (area_units * p.n_tiles);
+        int ux = 0;
+        raster_grouped(u, area_units, p.n_tiles, p.raster_g, ux, nt);
+        const int si = 1 + ux / band_units;
+        um = order[si] * p.seg_m_tiles + b * band_units + (ux - (si - 1) * band_units);
       }
     } else {
       const int b = pos / (p.R * per_band);

@@ -89,20 +89,37 @@ def warn_ignored(where: str, **given) -> None:
 
 
 class PlanCache:
+    """Plans of one context, keyed by operand addresses and shapes; least recently used out.
+
+    A plan bakes pointers into tensor maps, so a caller that hands in freshly allocated tensors
+    (new addresses) every call misses every time and pays the encoding again. ``hits`` / ``misses`` /
+    ``evictions`` make that visible; after ``4 * capacity`` evictions one warning says so."""
+
     def __init__(self, capacity: int = 64):
         self.capacity = capacity
         self._d: "OrderedDict[tuple, int]" = OrderedDict()
+        self.hits = self.misses = self.evictions = 0
+        self._warned = False
 
     def get(self, key: tuple, make) -> int:
         pid = self._d.get(key)
         if pid is not None:
             self._d.move_to_end(key)
+            self.hits += 1
             return pid
+        self.misses += 1
         pid = make()
         self._d[key] = pid
         if len(self._d) > self.capacity:
             _, old = self._d.popitem(last=False)
             native().gemm_plan_destroy(old)
+            self.evictions += 1
+            if self.evictions >= 4 * self.capacity and not self._warned:
+                self._warned = True
+                import warnings
+                warnings.warn("tridist_b200: a plan cache keeps evicting (operand addresses change from call to "
+                              "call, so tensor maps are re-encoded every time); reuse buffers across calls",
+                              stacklevel=3)
         return pid
 
     def clear(self) -> None:
