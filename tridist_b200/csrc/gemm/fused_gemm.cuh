@@ -622,7 +622,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
     for (int i = 0; i < kPushSlots; ++i) mbar_init(&push_bar[i], 1);
     s_flags[0] = 0;
     s_flags[1] = 1;
-    s_flags[2] = (pushes && !p.ag_mc) ? 0 : 1;   // (the multicast push keeps out of the operand ring)
+    s_flags[2] = pushes ? 0 : 1;   // a CTA that carries the transfer computes nothing until its part is out
     s_flags[3] = 0;
     mbar_fence_init();
   }
@@ -692,8 +692,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       const int up_row0 = p.swiglu_up_row0;
       const CUtensorMap* const bmap = &p.tma_b;
       const int ahead = p.l2_ahead;
-      if (pushes && !p.ag_mc) {
-        // the operand ring carries this CTA's part of the all-gather push first (the pushing
+      if (pushes) {
+        // the operand ring carries this CTA's part of the all-gather push first (the multicast
+        // form leaves the ring alone, but its loads and stores would starve this SM's operand
+        // feed just the same: the sending CTAs sit the transfer out as well) (the pushing
         // thread's own waits are bounded, so this one ends too; the limit is a backstop)
         const uint64_t t0 = globaltimer_ns();
         while (s_flags[2] == 0) {
@@ -1447,11 +1449,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
       // with the CTA's own operand loads.
       if (p.ag_mc) {
         // ---- multicast push: one store through the switch reaches every rank's workspace, so this
-        // rank sends its shard ONCE (not once per peer) and the work is small enough for the
-        // communication warps of all CTAs to do on the side: no CTA gives up tiles for it, no
-        // shared memory is involved. Chunk-major, each CTA a slice of every chunk, so that the
-        // first rows are complete everywhere first; the last CTA to finish its slice of a chunk
-        // raises that chunk's ticket on all peers.
+        // rank sends its shard ONCE (not once per peer). The communication warps of the first
+        // push_grid CTAs do it (registers only, no shared memory); those CTAs join the GEMM when
+        // their part is out, like the CTAs of the bulk-copy push, but there are fewer bytes to
+        // wait for. Chunk-major, each sending CTA a slice of every chunk, so that the first rows
+        // are complete everywhere first; the last CTA to finish its slice of a chunk raises that
+        // chunk's ticket on all peers.
         constexpr int kU = 8;                                        // 16-byte pieces in flight per thread
         const int64_t chunk_pieces = static_cast<int64_t>(p.chunk_rows) * p.K / 8;
         const int64_t per = (chunk_pieces + push_grid - 1) / push_grid;
@@ -1484,6 +1487,13 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p0, const GemmParams* __res
               for (int d = 0; d < p.R; ++d)
                 if (d != p.rank) st_release_sys(p.peer_ag_flags[d] + p.rank * p.ag_flag_stride + ck, p.round);
             }
+          }
+        }
+        if (pushes) {
+          named_bar_sync(1, kCommThreads);
+          if (ctid == 0) {
+            __threadfence_block();
+            s_flags[2] = 1;               // this CTA's producer may start
           }
         }
       } else if (ctid == 0) {

@@ -194,9 +194,11 @@ def _push_parts(chunk_rows: int, K: int) -> int:
     return parts
 
 
-def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int, want_ctas: int = 0):
+def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int, want_ctas: int = 0,
+               multicast: bool = False):
     """(pushing CTAs, scheduling rounds they sit out). The pushing CTAs carry the whole shard to
-    the peers before they compute anything; they skip as many rounds of tiles as that takes."""
+    the peers before they compute anything; they skip as many rounds of tiles as that takes.
+    ``multicast``: the shard leaves once, as multimem stores by the CTAs' communication warps."""
     m_tiles = M // BM
     wide = env_int("TRIDIST_WIDE", 1) and m_tiles >= 4 and (m_pr // BM) % 4 == 0
     pair = env_int("TRIDIST_CTA_PAIR", 1) and (m_pr // BM) % 2 == 0
@@ -205,14 +207,17 @@ def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int, want_
     units = ((M + unit_rows - 1) // unit_rows) * ((N_out + bn_out - 1) // bn_out)
     rounds = units / float(workers)
     tile_us = unit_rows * 256.0 * 2.0 * K / ((2 if pair else 1) * 8192.0 * 1500.0)
-    out_bytes = (R - 1) * m_pr * K * 2.0
+    out_bytes = (1 if multicast else R - 1) * m_pr * K * 2.0
+    # measured: about 34 GB/s per CTA of the bulk-copy push (twelve 16 KB pieces in flight), 560 GB/s at
+    # most; multimem stores (128 threads, eight 16-byte pieces each): 8, 16 and 24 CTAs all send 50 MB in
+    # 0.48-0.51 ms at 4 GPUs, so at least 13 GB/s per CTA and about 105 GB/s per GPU at most
+    per_cta, cap, max_ctas = (13.0, 105.0, 16) if multicast else (34.0, 560.0, 32)
     forced_ctas, forced_skip = env_int("TRIDIST_PUSH_CTAS", -1), env_int("TRIDIST_PUSH_SKIP", -1)
     if forced_ctas < 0 and want_ctas > 0:
         forced_ctas = want_ctas
 
     def push_us(ctas: int) -> float:
-        # measured: about 34 GB/s per pushing CTA (twelve 16 KB pieces in flight), 560 GB/s at most
-        return out_bytes / (min(ctas * 34.0, 560.0) * 1e3)
+        return out_bytes / (min(ctas * per_cta, cap) * 1e3)
 
     def skip_of(ctas: int) -> int:
         return max(0, min(int(math.ceil(push_us(ctas) / tile_us)), max(int(rounds) - 1, 0)))
@@ -223,8 +228,8 @@ def _push_plan(M: int, N_out: int, K: int, m_pr: int, R: int, bn_out: int, want_
         # fewest CTA-rounds given up to the push, among the counts that finish it by 60 % of the kernel
         step = 2 if pair else 1
         best = None
-        for n in range(4, 33, step):
-            if push_us(n) > 0.6 * rounds * tile_us and n < 32:
+        for n in range(4, max_ctas + 1, step):
+            if push_us(n) > 0.6 * rounds * tile_us and n < max_ctas:
                 continue
             cost = n * skip_of(n)
             if best is None or cost < best[0]:
@@ -276,10 +281,10 @@ def _plan(ctx, a, b, c, swiglu=False):
             # A subset of the CTAs carries the push (their operand ring is the copy ring
             # meanwhile) and joins the GEMM as many rounds late as the push takes.
             if ctx.transport == "mc":
-                # every CTA's communication warps send a slice; nobody sits out a round
                 d["nvls"] = 1
                 d["mc_part"] = [ctx.mc.mc_ptr, ctx.mc.mc_ptr + half]
-                d["push_ctas"], d["push_skip_rounds"] = 0, 0
+                d["push_ctas"], d["push_skip_rounds"] = _push_plan(M, N, K, m_pr, R, bn // 2 if swiglu else bn,
+                                                                   ctx.push_ctas, multicast=True)
                 if not d["seg_bands"] and baked_table is None and ctx.order_override is None:
                     # every source's rows arrive at the same rate: own rows first, then the first
                     # row unit of every source, then the second ...
