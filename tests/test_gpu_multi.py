@@ -32,6 +32,7 @@ def _all_ops(rank, R):
     for transport in ("auto", "push", "pull"):
         ctx = create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, rank, R, M_PER_CHUNK=256, transport=transport)
         assert ctx.transport == (transport if transport != "auto" else ("mc" if ctx.mc is not None else "push"))
+        assert ctx.mc is None or R > 2, "with one peer the bulk-copy push is the default"
         for it in range(4):
             a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, it, dt)
             a, b = a_all[rank].cuda(), b.cuda()

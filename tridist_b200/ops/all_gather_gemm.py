@@ -17,12 +17,13 @@ then loads it from the local workspace; tcgen05 tiles run own rows first, then s
 arrival order. There is no host-side synchronisation and no global barrier: the workspace
 is double-buffered by call parity.
 
-Transports (``transport=`` / ``TRIDIST_AG_TRANSPORT``; ``auto`` = ``mc`` where the fabric has
-multicast, else ``push``):
+Transports (``transport=`` / ``TRIDIST_AG_TRANSPORT``; ``auto`` = ``mc`` at three or more ranks where
+the fabric has multicast, else ``push``):
 
   mc    the workspace is bound to an NVSwitch multicast object and the shard leaves as
         ``multimem.st``: one store reaches every rank, so a rank sends its shard once instead of
-        once per peer, and the communication warps of all CTAs do it on the side
+        once per peer; the communication warps of a few CTAs do it (about 105 GB/s per GPU), and
+        those CTAs join the GEMM when their part is out
   push  bulk copies (16 KB pieces through a shared-memory ring) into each peer's workspace by a
         few CTAs that join the GEMM late
   pull  every rank stages its shard in its own workspace, the consumers copy it out of the peers'
@@ -113,7 +114,8 @@ def create_ag_gemm_intra_node_context(max_M, K, input_dtype, output_dtype, rank,
     want = transport or env_str("TRIDIST_AG_TRANSPORT", "auto")
     assert want in ("auto", "mc", "push", "pull")
     ws_bytes = 2 * max_M * K * 2
-    if num_ranks > 1 and want in ("auto", "mc") and env_int("TRIDIST_NVLS", 1):
+    # with one peer a multicast store saves no bytes and its rate is lower than the bulk copies'
+    if (num_ranks > 2 or want == "mc") and num_ranks > 1 and want in ("auto", "mc") and env_int("TRIDIST_NVLS", 1):
         ctx.mc = world.alloc_multicast(ws_bytes)
     if want == "mc" and ctx.mc is None:
         raise RuntimeError("tridist_b200: transport 'mc' needs a multicast-bound workspace: "
