@@ -167,3 +167,18 @@ def test_plan_cache_is_lru_and_reports_thrashing(monkeypatch):
         c.get(("x", 99), maker(99))
     c.clear()
     assert len(destroyed) == 1 + 7 + 2
+
+
+def test_transfer_plans_of_the_all_gather():
+    """How many CTAs carry the all-gather and how many rounds they sit out: the multicast form
+    sends the shard once, so it needs fewer CTA-rounds than the bulk-copy push from three ranks on."""
+    from tridist_b200.ops.all_gather_gemm import _push_plan
+    M, K = 8192, 12288
+    for R in (4, 8):
+        n_pr, m_pr = 49152 // R, M // R
+        mc = _push_plan(M, n_pr, K, m_pr, R, 256, multicast=True)
+        push = _push_plan(M, n_pr, K, m_pr, R, 256)
+        assert 4 <= mc[0] <= 16 and 4 <= push[0] <= 32 and mc[0] % 2 == 0 and push[0] % 2 == 0
+        assert mc[0] * mc[1] <= push[0] * push[1], (R, mc, push)
+    # a forced CTA count is honoured, the rounds follow from it
+    assert _push_plan(M, 6144, K, 1024, 8, 256, want_ctas=12)[0] == 12
