@@ -748,3 +748,32 @@ def test_gemm_ar_rd_ack_wait_runs_out():
     w.check()
     ref = sum(a_all[s].float() @ b_all[s].float().t() for s in range(R))
     assert (c_list[0].float() - ref).abs().max().item() < 2e-2 and torch.equal(c_list[0], c_list[1])
+
+
+def test_own_first_band_walk_emulated():
+    """The walk the multicast all-gather uses (own rows, then row unit b of every other source before
+    unit b + 1 of any) on virtual ranks with the bulk-copy push: only the order of the tiles changes,
+    the result is bit-identical to the source-major walk."""
+    from tridist_b200.ops.all_gather_gemm import ag_gemm_emulated, create_ag_gemm_intra_node_context
+    R = 4
+    w = _emu(R)
+    dt = torch.bfloat16
+    m_pr, K, n_pr = 1024, 256, 512
+    ctxs = [create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, r, R, M_PER_CHUNK=256, world=w) for r in range(R)]
+    a = [_rand((m_pr, K), 700 + r, dt) for r in range(R)]
+    b = [_rand((n_pr, K), 710 + r, dt) for r in range(R)]
+    ref = [torch.empty(m_pr * R, n_pr, dtype=dt, device="cuda") for _ in range(R)]
+    ag_gemm_emulated(ctxs, a, b, ref)
+    torch.cuda.synchronize()
+    w.check()
+    assert (ref[1].float() - torch.cat(a, 0).float() @ b[1].float().t()).abs().max().item() < 2e-2
+    for ctx in ctxs:
+        ctx.seg_bands, ctx.seg_own_first = -1, 1
+        ctx.plans.clear()
+    for it in range(2):                              # both workspace parities
+        out = [torch.empty_like(x) for x in ref]
+        ag_gemm_emulated(ctxs, a, b, out)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(R):
+            assert torch.equal(out[r], ref[r]), (it, r)

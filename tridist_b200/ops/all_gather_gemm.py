@@ -253,7 +253,7 @@ def _plan(ctx, a, b, c, swiglu=False):
     baked_table = getattr(ctx, "emu_order_table", None)
     key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), m_pr, n_rows, K, a.stride(0), b.stride(0), c.stride(0),
            a.dtype, swiglu, bn, tuple(order), baked_table.data_ptr() if baked_table is not None else 0,
-           ctx.observe, getattr(ctx, "emu_table_header", False), getattr(ctx, "seg_bands", 0), ctx.transport,
+           ctx.observe, getattr(ctx, "emu_table_header", False), getattr(ctx, "seg_bands", 0), getattr(ctx, "seg_own_first", 0), ctx.transport,
            ctx.push_ctas)
 
     def make():
@@ -266,6 +266,7 @@ def _plan(ctx, a, b, c, swiglu=False):
             d["order_table"] = baked_table.data_ptr()
             d["order_table_header"] = 1 if getattr(ctx, "emu_table_header", False) else 0
         d["seg_bands"] = int(getattr(ctx, "seg_bands", 0) or 0)
+        d["seg_own_first"] = int(getattr(ctx, "seg_own_first", 0) or 0)
         if swiglu:
             d["epi"] = EPI_SWIGLU
             d["swiglu_up_row0"] = N

@@ -79,6 +79,8 @@ def create_gemm_rs_intra_node_context(max_M, N, output_dtype, rank, num_ranks, m
     if isinstance(world, CpuWorld):
         return ctx
     ctx.mode = env_str("TRIDIST_RS_MODE", "auto")
+    ctx.reduce_ctas = env_int("TRIDIST_RS_REDUCE_CTAS", 0)
+    ctx.reduce_tail = env_int("TRIDIST_RS_REDUCE_TAIL", 0)
     if num_ranks > 1:
         ctx.slots = world.alloc(2 * max_M * N * 2, rank)
         ctx.tile_flags = world.alloc(num_ranks * ctx.max_tiles * 4, rank)

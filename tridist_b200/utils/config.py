@@ -23,6 +23,8 @@ TRIDIST_RD_TRANSPORT      "rd" (default: panel exchange with XOR partners) | "me
                           for the gemm_ar_rd entry points; TRIDIST_RD_CTAS = CTAs of the exchange kernel (16)
 TRIDIST_RS_MODE           "auto" | "slots" | "nvls": reduce-scatter through peer-written slots or through the
                           switch (multimem.ld_reduce by the owner); auto = nvls wherever a multicast buffer exists
+TRIDIST_RS_REDUCE_CTAS    switch-reduced reduce-scatter: CTAs whose communication warps reduce during the mainloop
+                          (default 0 = all); TRIDIST_RS_REDUCE_TAIL = last blocks every CTA helps with
 TRIDIST_DEBUG             1: before a plan is created, replay its tile schedule on the host and check every
                           ticket index and buffer offset against the buffers' sizes (nothing is launched)
 TRIDIST_CHECK_RESIDENCY   0: skip the check at plan creation that the whole grid of a kernel whose CTAs wait on
