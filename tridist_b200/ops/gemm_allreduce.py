@@ -208,6 +208,12 @@ def _plan(ctx, a, b, c, mode, parity):
             d["slot_stride"] = M * N
             d["peer_tile_flags"] = ctx.tile_flags.ptrs()
             d["ticket_stride"] = ctx.max_tiles       # one word per (source, tile) for every M
+        if op in (OP_AR1, OP_AR2) and ((M + 255) // 256) * ((N + 255) // 256) <= 16 * 74:
+            # Few rounds of tiles: 256 x 256 pair tiles instead of 512 x 256. The reduce of a tile
+            # starts when the tile is done, so twice as many, half as long rounds hide more of the
+            # all-reduce behind the mainloop than the wide tile saves in operand traffic
+            # (4 GPUs, K 28672, N 8192: M = 1024 0.151 ms against 0.169, M = 4096 0.428 against 0.445).
+            d["allow_wide"] = 0
         if op == OP_AR2:
             d["sched"] = SCHED_STRIDED
             d["seg_order"] = rotation_order(rank, R, 1, own_last=True)
