@@ -29,10 +29,11 @@ def _all_ops(rank, R):
     m_pr, K, n_pr = 512, 1024, 768
     # every transport: multicast stores through the switch (what "auto" picks where the fabric has
     # multicast), bulk-copy push, pull
-    for transport in ("auto", "push", "pull"):
+    from tridist_b200.parallel.runtime import native
+    has_mc = bool(native().vmm_multicast_supported()[0]) if hasattr(native(), "vmm_multicast_supported") else False
+    for transport in ("auto", "pull") + (("mc",) if has_mc else ()):
         ctx = create_ag_gemm_intra_node_context(m_pr * R, K, dt, dt, rank, R, M_PER_CHUNK=256, transport=transport)
-        assert ctx.transport == (transport if transport != "auto" else ("mc" if ctx.mc is not None else "push"))
-        assert ctx.mc is None or R > 2, "with one peer the bulk-copy push is the default"
+        assert ctx.transport == ("push" if transport == "auto" else transport)
         for it in range(4):
             a_all, b = ag_inputs(rank, R, m_pr, K, n_pr, it, dt)
             a, b = a_all[rank].cuda(), b.cuda()

@@ -17,8 +17,8 @@ TRIDIST_PUSH_CTAS         CTAs that drive the all-gather push (default: from the
                           GEMM takes, 34 GB/s per CTA up to the link's 560 GB/s; 0 = all)
 TRIDIST_PUSH_SKIP         scheduling rounds the pushing CTAs sit out (default: what their push costs them)
 TRIDIST_AG_TICKET_ROWS    rows of a gathered shard covered by one arrival ticket (default 256)
-TRIDIST_AG_TRANSPORT      "auto" | "mc" | "push" | "pull": how the all-gather shard travels (auto = multicast
-                          stores through the switch where the fabric has them, else the bulk-copy push)
+TRIDIST_AG_TRANSPORT      "auto" | "push" | "mc" | "pull": how the all-gather shard travels (auto = push: bulk copies
+                          by a few CTAs; mc = multicast stores through the switch; pull = consumers copy)
 TRIDIST_RD_TRANSPORT      "rd" (default: panel exchange with XOR partners) | "mesh" (the fused all-reduce kernel)
                           for the gemm_ar_rd entry points; TRIDIST_RD_CTAS = CTAs of the exchange kernel (16)
 TRIDIST_RS_MODE           "auto" | "slots" | "nvls": reduce-scatter through peer-written slots or through the
