@@ -130,7 +130,7 @@ def alloc_symmetric_multicast(C, rank: int, num_ranks: int, group, nbytes: int) 
         why = f"{type(exc).__name__}: {exc}"
     errs = _agree(group, why, num_ranks)
     if not any(errs):
-        try:   # round 1: every rank offers its allocation to every peer
+        try:   # first exchange: every rank offers its allocation to every peer
             received = exchange_fds(rank, num_ranks, token, 1, own_fd, num_ranks - 1,
                                     [r for r in range(num_ranks) if r != rank])
             for src, fd in received.items():
@@ -142,7 +142,7 @@ def alloc_symmetric_multicast(C, rank: int, num_ranks: int, group, nbytes: int) 
             why = f"{type(exc).__name__}: {exc}"
         errs = _agree(group, why, num_ranks)
     if not any(errs):
-        try:   # round 2: rank 0 creates the multicast object and offers it to the others
+        try:   # second exchange: rank 0 creates the multicast object and offers it to the others
             if rank == 0:
                 alloc.mc_handle = int(C.vmm_mc_create(alloc.nbytes, num_ranks))
                 mc_fd = int(C.vmm_export_fd(alloc.mc_handle))
