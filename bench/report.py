@@ -6,21 +6,43 @@
 Per workload and GPU count: fused p50 / cuBLAS+NCCL p50 (speed-up), and the roofline fraction at the
 largest GPU count; then the step times with the strong-scaling efficiency relative to the smallest
 GPU count present. Files that carry a `note` have it printed under the table.
+
+`--override FILE` (repeatable) takes the per-operator cells that FILE holds (a `bench.py --ops ...` line of
+the same GPU count) in place of those of the full run and marks them with a dagger: a transport or knob
+that was measured separately, in the same call, shows up in the table without touching the recorded lines.
+
+  python bench/report.py bench/results/bench_{1,2,4,8}xB200.json \\
+         --override bench/results/bench_4xB200_ag_push.json --override bench/results/bench_8xB200_ag_push.json
 """
 from __future__ import annotations
 
 import json
+import math
 import sys
 from typing import Dict, List
 
 
-def load(paths: List[str]) -> Dict[int, Dict]:
+def _read(p: str) -> Dict:
+    with open(p) as fh:
+        text = fh.read().strip()
+    return json.loads(text if text.startswith("{") and "\n{" not in text else text.splitlines()[-1])
+
+
+def load(paths: List[str], overrides: List[str] = ()) -> Dict[int, Dict]:
     runs = {}
     for p in paths:
-        with open(p) as fh:
-            text = fh.read().strip()
-        line = json.loads(text if text.startswith("{") and "\n{" not in text else text.splitlines()[-1])
+        line = _read(p)
         runs[int(line["n_gpus"])] = line
+    for p in overrides:
+        line = _read(p)
+        n = int(line["n_gpus"])
+        if n not in runs:
+            continue
+        for name, cell in line.get("ops", {}).items():
+            runs[n].setdefault("ops", {})[name] = dict(cell, overridden=True)
+        sps = [c["speedup_vs_cublas_nccl"] for c in runs[n]["ops"].values() if "speedup_vs_cublas_nccl" in c]
+        if sps:
+            runs[n]["vs_baseline"] = round(math.exp(sum(math.log(x) for x in sps) / len(sps)), 3)
     return dict(sorted(runs.items()))
 
 
@@ -41,7 +63,8 @@ def tables(runs: Dict[int, Dict]) -> str:
                 cells.append("-")
                 continue
             base, sp = op.get("cublas_nccl_p50_ms"), op.get("speedup_vs_cublas_nccl")
-            cells.append(f"{op['fused_p50_ms']:.3f}" + (f" / {base:.3f} ({sp:.2f})" if base is not None else ""))
+            cells.append(f"{op['fused_p50_ms']:.3f}" + (f" / {base:.3f} ({sp:.2f})" if base is not None else "")
+                         + (" †" if op.get("overridden") else ""))
         frac = runs[ns[-1]].get("ops", {}).get(name, {}).get("roofline_frac")
         lines.append(f"| {name} | " + " | ".join(cells) + f" | {frac if frac is not None else '-'} |")
     out = ["Fused p50 ms / cuBLAS+NCCL p50 ms (speed-up):", ""] + lines + [""]
@@ -63,9 +86,15 @@ def tables(runs: Dict[int, Dict]) -> str:
 
 
 def main():
-    if len(sys.argv) < 2:
+    args = sys.argv[1:]
+    overrides = []
+    while "--override" in args:
+        i = args.index("--override")
+        overrides.append(args[i + 1])
+        del args[i:i + 2]
+    if not args:
         sys.exit(__doc__)
-    print(tables(load(sys.argv[1:])))
+    print(tables(load(args, overrides)))
 
 
 if __name__ == "__main__":
