@@ -182,3 +182,29 @@ def test_transfer_plans_of_the_all_gather():
         assert mc[0] * mc[1] <= push[0] * push[1], (R, mc, push)
     # a forced CTA count is honoured, the rounds follow from it
     assert _push_plan(M, 6144, K, 1024, 8, 256, want_ctas=12)[0] == 12
+
+
+def test_report_tables_and_overrides(tmp_path):
+    """bench/report.py: one recorded line per GPU count becomes the scaling table; an override file
+    replaces the cells it holds, marks them and re-derives the geometric mean."""
+    import json
+
+    from bench.report import load, tables
+
+    def line(n, ops, step):
+        return {"n_gpus": n, "ms_per_step": step, "vs_baseline": 1.0, "e2e": {"value": 2 * step},
+                "clocks": {"sm_mhz": 1500.0, "reasons": []},
+                "ops": {k: {"fused_p50_ms": f, "cublas_nccl_p50_ms": b, "speedup_vs_cublas_nccl": round(b / f, 3),
+                            "roofline_frac": 0.5} for k, (f, b) in ops.items()}}
+
+    f1, f8, fo = tmp_path / "b1.json", tmp_path / "b8.json", tmp_path / "o8.json"
+    f1.write_text(json.dumps(line(1, {"ag_gemm": (8.0, 8.0), "gemm_rs": (8.0, 8.8)}, 16.0)))
+    f8.write_text(json.dumps(line(8, {"ag_gemm": (1.2, 1.14), "gemm_rs": (1.0, 1.1)}, 2.2)))
+    fo.write_text(json.dumps(line(8, {"ag_gemm": (1.0, 1.14)}, 1.0)))
+    runs = load([str(f8), str(f1)], [str(fo)])
+    assert list(runs) == [1, 8]
+    assert runs[8]["ops"]["ag_gemm"]["fused_p50_ms"] == 1.0 and runs[8]["ops"]["ag_gemm"]["overridden"]
+    assert abs(runs[8]["vs_baseline"] - (1.14 * 1.1) ** 0.5) < 2e-3
+    text = tables(runs)
+    assert "| ag_gemm | 8.000 / 8.000 (1.00) | 1.000 / 1.140 (1.14) † | 0.5 |" in text
+    assert "| 8 | 2.200 | 4.4 | 0.91 |" in text          # 16 / (2.2 * 8)
